@@ -1,0 +1,111 @@
+/*
+ * tgo_mmq.h - C ABI of the sm_100a quantized-weight matmul library (libtgo_mmq.so).
+ *
+ * This is the boundary a host layer binds instead of the reference's ROCm extension
+ * (csrc/mmq_hip.cu): one entry point per native operator body.  Plain pointers and sizes only;
+ * every pointer is a device pointer on the current CUDA device unless stated otherwise; every
+ * call is asynchronous on `stream` (a cudaStream_t passed as void*), performs no host
+ * synchronisation and no device-to-host read, borrows its inputs and writes only its outputs
+ * and workspace.  Return value: 0 on success, a negative TGO_E_* code otherwise, with a
+ * human-readable message available from tgo_last_error() on the calling thread.
+ *
+ * Tensor conventions (reference: csrc/mmq_hip.cu:325-406, 587-631):
+ *   activations / outputs / gradients: bf16, row-major, contiguous, 16-byte aligned;
+ *   packed weights: raw GGUF super-blocks, uint8, row n = K/256 consecutive blocks, 16-byte
+ *   aligned; grouped weights are [E][N][K/256 * block_bytes];
+ *   quant types use the GGML ids (Q3_K 11, Q4_K 12, Q5_K 13, Q6_K 14, IQ2_S 22);
+ *   K must be a positive multiple of 256;
+ *   routing metadata: expert_indices int64[G], expert_offsets int32[G] = cumulative END row of
+ *   each group (group g covers rows [offsets[g-1], offsets[g]), offsets[-1] = 0).  A group with
+ *   an out-of-range expert id or an empty / out-of-range row span is skipped on the device and
+ *   its output rows are left untouched (reference: csrc/mmq_core.cuh:468-476).
+ */
+#ifndef TGO_MMQ_H_
+#define TGO_MMQ_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TGO_OK 0
+#define TGO_E_ARG (-1)      /* bad argument (null pointer, size, alignment, type) */
+#define TGO_E_CUDA (-2)     /* a CUDA runtime / driver call failed */
+#define TGO_E_WORKSPACE (-3) /* workspace too small */
+#define TGO_E_DEVICE (-4)   /* a kernel reported a timed-out wait (see tgo_device_status) */
+
+#define TGO_Q3_K 11
+#define TGO_Q4_K 12
+#define TGO_Q5_K 13
+#define TGO_Q6_K 14
+#define TGO_IQ2_S 22
+
+/* Library version (major*10000 + minor*100 + patch). */
+int tgo_version(void);
+
+/* Message of the last failing call on this thread ("" if none). */
+const char* tgo_last_error(void);
+
+/* Bytes of one 256-weight super-block of `quant_type`, or -1 if unsupported.
+ * Replaces packed_block_bytes (csrc/mmq_hip.cu:38-48). */
+int64_t tgo_block_bytes(int quant_type);
+
+/* Reads (synchronously) and clears the device status word that kernels set when a bounded wait
+ * gives up.  *status = 0 means no kernel ever gave up.  No counterpart in the reference (its
+ * kernels have no inter-warp waits). */
+int tgo_device_status(int* status);
+
+/* Decode n_blocks consecutive super-blocks to bf16 (round-to-nearest-even), 256 values each.
+ * The same device decoders feed the matmul kernels; exposed for bit-exact checks against
+ * decode_gguf_value (csrc/ck/gguf_decode.cuh:54-149). */
+int tgo_dequantize_bf16(const void* packed, int64_t n_blocks, int quant_type, void* out_bf16,
+                        void* stream);
+
+/* Dense forward  Y[M,N] = X[M,K] * W[N,K]^T.
+ * Replaces the device work of mmq_cuda -> launch_dense_mmq (csrc/mmq_hip.cu:117-147, 587-678). */
+int tgo_mmq_fwd(const void* x, const void* packed_weight, void* y, int64_t rows,
+                int64_t out_features, int64_t in_features, int quant_type, void* stream);
+
+/* Dense input gradient  dX[M,K] = dY[M,N] * W[N,K].
+ * Replaces mmq_grad_input_cuda -> ck::launch_dense_mmq_grad_input
+ * (csrc/mmq_hip.cu:680-774, csrc/ck/mmq_backward.cuh:1066-1241). */
+int tgo_mmq_dx(const void* dy, const void* packed_weight, void* dx, int64_t rows,
+               int64_t out_features, int64_t in_features, int quant_type, void* stream);
+
+/* Workspace bytes the grouped calls below need for `rows` routed rows in `num_groups` groups
+ * (the device-built tile list; reference: new_grouped_row_task_workspace,
+ * csrc/mmq_hip.cu:544-558). */
+int64_t tgo_grouped_workspace_bytes(int64_t rows, int64_t num_groups);
+
+/* Builds the tile list (device prefix sum over the groups) into `workspace`.  The grouped calls
+ * below do this themselves; exposed for tests.  Replaces grouped_mmq_build_row_tasks
+ * (csrc/mmq_core.cuh:516-571). */
+int tgo_build_tiles(const int64_t* expert_indices, const int32_t* expert_offsets,
+                    int64_t num_groups, int64_t num_experts, int64_t rows, void* workspace,
+                    int64_t workspace_bytes, void* stream);
+
+/* Grouped forward over expert-sorted rows; with w1/y1 non-null also the second projection of a
+ * gate/up pair from the same activations (y0 = X*W0[e]^T, y1 = X*W1[e]^T).
+ * Replaces grouped_mmq_cuda and grouped_mmq_pair_cuda (csrc/mmq_hip.cu:954-1193). */
+int tgo_grouped_fwd(const void* x, const void* w0, const void* w1, void* y0, void* y1,
+                    const int64_t* expert_indices, const int32_t* expert_offsets,
+                    int64_t num_groups, int64_t num_experts, int64_t rows, int64_t out_features,
+                    int64_t in_features, int quant_type, void* workspace, int64_t workspace_bytes,
+                    void* stream);
+
+/* Grouped input gradient dX = dY0*W0[e] (+ dY1*W1[e] when dy1/w1 are non-null; both products
+ * are summed in fp32 before the single bf16 rounding).
+ * Replaces grouped_mmq_grad_input_cuda and grouped_mmq_pair_grad_input_cuda
+ * (csrc/mmq_hip.cu:776-952, csrc/ck/grouped_mmq_backward.cuh:154-306, 460-568). */
+int tgo_grouped_dx(const void* dy0, const void* dy1, const void* w0, const void* w1, void* dx,
+                   const int64_t* expert_indices, const int32_t* expert_offsets,
+                   int64_t num_groups, int64_t num_experts, int64_t rows, int64_t out_features,
+                   int64_t in_features, int quant_type, void* workspace, int64_t workspace_bytes,
+                   void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TGO_MMQ_H_ */

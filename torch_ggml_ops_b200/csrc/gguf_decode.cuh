@@ -1,0 +1,241 @@
+// Device-side decode of raw GGUF super-blocks (256 weights) to bf16, 32 weights at a time.
+//
+// The value produced for each weight is bf16_rne(w) with w the fp32 value the reference's
+// decoder defines (reference: csrc/ck/gguf_decode.cuh:54-149; block field offsets
+// csrc/vendor/llama_cpp/common.cuh:78-127).  Every product below is exact in fp32 (fp16
+// super-scale x small integers), the only fp32 rounding is the Q4_K / Q5_K subtraction of the
+// minimum, so the order of the exact operations is free and the result is bit-identical.
+//
+// A block is read from a shared-memory "window": the 16-byte-aligned span of global memory that
+// covers it, copied verbatim.  Blocks of 110 / 210 / 82 bytes start on 2-byte boundaries only, so
+// their fields are fetched as aligned 32-bit words and funnel-shifted into place.
+#pragma once
+
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace tgo {
+
+enum : int { QT_Q3_K = 11, QT_Q4_K = 12, QT_Q5_K = 13, QT_Q6_K = 14, QT_IQ2_S = 22 };
+
+template <int QT> struct BlockFmt;
+// kBytes: block size.  kAligned: every block starts 16-byte aligned.  kCopy: bytes copied per
+// block window (covers the block from the aligned address below its start).  kSlot: distance
+// between windows in shared memory (kCopy plus slack for the trailing funnel-shift word).
+template <> struct BlockFmt<QT_Q4_K> { static constexpr int kBytes = 144, kAligned = 1, kCopy = 144, kSlot = 144; };
+template <> struct BlockFmt<QT_Q5_K> { static constexpr int kBytes = 176, kAligned = 1, kCopy = 176, kSlot = 176; };
+template <> struct BlockFmt<QT_Q6_K> { static constexpr int kBytes = 210, kAligned = 0, kCopy = 224, kSlot = 240; };
+template <> struct BlockFmt<QT_Q3_K> { static constexpr int kBytes = 110, kAligned = 0, kCopy = 128, kSlot = 144; };
+template <> struct BlockFmt<QT_IQ2_S> { static constexpr int kBytes = 82, kAligned = 0, kCopy = 96, kSlot = 112; };
+
+__host__ __device__ constexpr int block_bytes_of(int qt) {
+    return qt == QT_Q3_K ? 110 : qt == QT_Q4_K ? 144 : qt == QT_Q5_K ? 176 : qt == QT_Q6_K ? 210
+         : qt == QT_IQ2_S ? 82 : -1;
+}
+
+// N consecutive 32-bit words starting at a 2-byte-aligned shared-memory address.
+template <int N>
+__device__ __forceinline__ void ld_words(const uint8_t* p, uint32_t (&w)[N]) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t* base = reinterpret_cast<const uint32_t*>(a & ~static_cast<uintptr_t>(3));
+    const uint32_t sh = (static_cast<uint32_t>(a) & 2u) * 8u;
+    uint32_t prev = base[0];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        const uint32_t next = base[i + 1];
+        w[i] = __funnelshift_r(prev, next, sh);
+        prev = next;
+    }
+}
+__device__ __forceinline__ uint32_t ld_u16(const uint8_t* p) {
+    return *reinterpret_cast<const uint16_t*>(p);
+}
+__device__ __forceinline__ float half_bits_to_float(uint32_t h) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
+}
+// Byte b of v as an exact float: 2^23 + byte, minus 2^23.
+__device__ __forceinline__ float byte_to_float(uint32_t v, int b) {
+    return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650u + b)) - 8388608.0f;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// 6-bit scale and minimum of 32-weight group g from the 12 packed bytes of Q4_K / Q5_K, given as
+// three little-endian words (reference: csrc/ck/gguf_decode.cuh:13-31).
+__device__ __forceinline__ void kquant_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int g,
+                                                 int& sc, int& mn) {
+    const int j = g & 3;
+    const uint32_t a = (s0 >> (8 * j)) & 0xFFu;  // scales[j]
+    const uint32_t b = (s1 >> (8 * j)) & 0xFFu;  // scales[4 + j]
+    const uint32_t c = (s2 >> (8 * j)) & 0xFFu;  // scales[8 + j]
+    if (g < 4) {
+        sc = a & 63;
+        mn = b & 63;
+    } else {
+        sc = (c & 15) | ((a >> 2) & 0x30);
+        mn = (c >> 4) | ((b >> 2) & 0x30);
+    }
+}
+
+// Eight weights from two words of byte-sized quants: w = ds * q - mn.
+__device__ __forceinline__ uint4 affine8(uint32_t v0, uint32_t v1, float ds, float mn) {
+    uint4 o;
+    o.x = pack_bf16(ds * byte_to_float(v0, 0) - mn, ds * byte_to_float(v0, 1) - mn);
+    o.y = pack_bf16(ds * byte_to_float(v0, 2) - mn, ds * byte_to_float(v0, 3) - mn);
+    o.z = pack_bf16(ds * byte_to_float(v1, 0) - mn, ds * byte_to_float(v1, 1) - mn);
+    o.w = pack_bf16(ds * byte_to_float(v1, 2) - mn, ds * byte_to_float(v1, 3) - mn);
+    return o;
+}
+// Eight weights from two words of byte-sized quants with an integer offset: w = ds * (q - off).
+__device__ __forceinline__ uint4 scaled8(uint32_t v0, uint32_t v1, float ds, float off) {
+    uint4 o;
+    o.x = pack_bf16(ds * (byte_to_float(v0, 0) - off), ds * (byte_to_float(v0, 1) - off));
+    o.y = pack_bf16(ds * (byte_to_float(v0, 2) - off), ds * (byte_to_float(v0, 3) - off));
+    o.z = pack_bf16(ds * (byte_to_float(v1, 0) - off), ds * (byte_to_float(v1, 1) - off));
+    o.w = pack_bf16(ds * (byte_to_float(v1, 2) - off), ds * (byte_to_float(v1, 3) - off));
+    return o;
+}
+
+// decode32<QT>: weights 32g .. 32g+31 of the block at `blk` (shared memory), as four 16-byte
+// chunks of 8 bf16 each.  `grid` is the IQ2_S codebook in shared memory (unused otherwise).
+template <int QT>
+__device__ __forceinline__ void decode32(const uint8_t* blk, int g, const uint64_t* grid,
+                                         uint4 (&out)[4]);
+
+template <>
+__device__ __forceinline__ void decode32<QT_Q4_K>(const uint8_t* blk, int g, const uint64_t*,
+                                                  uint4 (&out)[4]) {
+    const uint4 head = *reinterpret_cast<const uint4*>(blk);  // d, dmin, scales[12]
+    int sc, mn;
+    kquant_scale_min(head.y, head.z, head.w, g, sc, mn);
+    const float ds = half_bits_to_float(head.x & 0xFFFFu) * static_cast<float>(sc);
+    const float dm = half_bits_to_float(head.x >> 16) * static_cast<float>(mn);
+    const uint4* qs = reinterpret_cast<const uint4*>(blk + 16 + (g >> 1) * 32);
+    const uint4 a = qs[0], b = qs[1];
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const int sh = 4 * (g & 1);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t v0 = (w[2 * c] >> sh) & 0x0F0F0F0Fu;
+        const uint32_t v1 = (w[2 * c + 1] >> sh) & 0x0F0F0F0Fu;
+        out[c] = affine8(v0, v1, ds, dm);
+    }
+}
+
+template <>
+__device__ __forceinline__ void decode32<QT_Q5_K>(const uint8_t* blk, int g, const uint64_t*,
+                                                  uint4 (&out)[4]) {
+    const uint4 head = *reinterpret_cast<const uint4*>(blk);
+    int sc, mn;
+    kquant_scale_min(head.y, head.z, head.w, g, sc, mn);
+    const float ds = half_bits_to_float(head.x & 0xFFFFu) * static_cast<float>(sc);
+    const float dm = half_bits_to_float(head.x >> 16) * static_cast<float>(mn);
+    const uint4* qh = reinterpret_cast<const uint4*>(blk + 16);
+    const uint4 ha = qh[0], hb = qh[1];
+    const uint32_t h[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+    const uint4* qs = reinterpret_cast<const uint4*>(blk + 48 + (g >> 1) * 32);
+    const uint4 a = qs[0], b = qs[1];
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const int sh = 4 * (g & 1);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t v0 = ((w[2 * c] >> sh) & 0x0F0F0F0Fu) | (((h[2 * c] >> g) & 0x01010101u) << 4);
+        const uint32_t v1 =
+            ((w[2 * c + 1] >> sh) & 0x0F0F0F0Fu) | (((h[2 * c + 1] >> g) & 0x01010101u) << 4);
+        out[c] = affine8(v0, v1, ds, dm);
+    }
+}
+
+template <>
+__device__ __forceinline__ void decode32<QT_Q6_K>(const uint8_t* blk, int g, const uint64_t*,
+                                                  uint4 (&out)[4]) {
+    // weights i = 32g + j: chunk c = g>>2 of 128; ql byte c*64 + (g&1)*32 + j, nibble (g&3)>>1;
+    // qh byte c*32 + j, bit pair g&3; one int8 scale per 16 weights.
+    const int c128 = g >> 2;
+    uint32_t ql[8], qh[8];
+    ld_words<8>(blk + c128 * 64 + (g & 1) * 32, ql);
+    ld_words<8>(blk + 128 + c128 * 32, qh);
+    const uint32_t sc2 = ld_u16(blk + 192 + 2 * g);
+    const float d = half_bits_to_float(ld_u16(blk + 208));
+    const float ds0 = d * static_cast<float>(static_cast<int>(static_cast<int8_t>(sc2 & 0xFFu)));
+    const float ds1 = d * static_cast<float>(static_cast<int>(static_cast<int8_t>(sc2 >> 8)));
+    const int sl = 4 * ((g & 3) >> 1);
+    const int shh = 2 * (g & 3);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t v0 = ((ql[2 * c] >> sl) & 0x0F0F0F0Fu) | (((qh[2 * c] >> shh) & 0x03030303u) << 4);
+        const uint32_t v1 =
+            ((ql[2 * c + 1] >> sl) & 0x0F0F0F0Fu) | (((qh[2 * c + 1] >> shh) & 0x03030303u) << 4);
+        out[c] = scaled8(v0, v1, c < 2 ? ds0 : ds1, 32.0f);
+    }
+}
+
+template <>
+__device__ __forceinline__ void decode32<QT_Q3_K>(const uint8_t* blk, int g, const uint64_t*,
+                                                  uint4 (&out)[4]) {
+    // weights i = 32g + j: low 2 bits qs[(g>>2)*32 + j] >> 2*(g&3); hmask[j] bit g set means
+    // "do not subtract 4"; 6-bit scale (minus 32) per 16 weights.
+    uint32_t hm[8], qs[8], s[3];
+    ld_words<8>(blk, hm);
+    ld_words<8>(blk + 32 + (g >> 2) * 32, qs);
+    ld_words<3>(blk + 96, s);
+    const float d = half_bits_to_float(ld_u16(blk + 108));
+    float ds[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int sg = 2 * g + t;  // 16-weight group 0..15
+        const int k = sg & 7;
+        const uint32_t lsb = ((k < 4 ? s[0] : s[1]) >> (8 * (k & 3))) & 0xFFu;  // scales[sg & 7]
+        const uint32_t ls = sg < 8 ? lsb : (lsb >> 4);
+        const uint32_t hs = ((s[2] >> (8 * (sg & 3))) & 0xFFu) >> (2 * (sg >> 2));
+        const int scale = static_cast<int>((ls & 15u) | ((hs & 3u) << 4)) - 32;
+        ds[t] = d * static_cast<float>(scale);
+    }
+    const int sq = 2 * (g & 3);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t v0 = ((qs[2 * c] >> sq) & 0x03030303u) | (((hm[2 * c] >> g) & 0x01010101u) << 2);
+        const uint32_t v1 =
+            ((qs[2 * c + 1] >> sq) & 0x03030303u) | (((hm[2 * c + 1] >> g) & 0x01010101u) << 2);
+        out[c] = scaled8(v0, v1, c < 2 ? ds[0] : ds[1], 4.0f);
+    }
+}
+
+template <>
+__device__ __forceinline__ void decode32<QT_IQ2_S>(const uint8_t* blk, int g, const uint64_t* grid,
+                                                   uint4 (&out)[4]) {
+    // weights 32g..32g+31 = codebook groups 4g..4g+3 of 8 weights: index qs[gg] | 2 bits of
+    // qh[g] << 8, sign byte qs[32 + gg]; one 4-bit scale per 16 weights in scales[g].
+    uint32_t idxw[1], sgnw[1];
+    ld_words<1>(blk + 2 + 4 * g, idxw);
+    ld_words<1>(blk + 34 + 4 * g, sgnw);
+    const uint32_t qh = blk[66 + g];
+    const uint32_t scb = blk[74 + g];
+    const float d = half_bits_to_float(ld_u16(blk));
+    const float db0 = (d * (0.5f + static_cast<float>(scb & 15u))) * 0.25f;
+    const float db1 = (d * (0.5f + static_cast<float>(scb >> 4))) * 0.25f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t idx = ((idxw[0] >> (8 * c)) & 0xFFu) | (((qh >> (2 * c)) & 3u) << 8);
+        const uint64_t mags = grid[idx];
+        const uint32_t m0 = static_cast<uint32_t>(mags), m1 = static_cast<uint32_t>(mags >> 32);
+        const uint32_t sg = (sgnw[0] >> (8 * c)) & 0xFFu;
+        const float db = c < 2 ? db0 : db1;
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float mag = byte_to_float(e < 4 ? m0 : m1, e & 3);
+            const float w = db * mag;
+            v[e] = __uint_as_float(__float_as_uint(w) ^ (((sg >> e) & 1u) << 31));
+        }
+        out[c].x = pack_bf16(v[0], v[1]);
+        out[c].y = pack_bf16(v[2], v[3]);
+        out[c].z = pack_bf16(v[4], v[5]);
+        out[c].w = pack_bf16(v[6], v[7]);
+    }
+}
+
+}  // namespace tgo

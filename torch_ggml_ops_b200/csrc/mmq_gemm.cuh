@@ -1,0 +1,484 @@
+// The quantized-weight GEMM kernel for sm_100a: one persistent, warp-specialised kernel that
+// serves dense, grouped and paired products in both directions.
+//
+//   forward  (kFwd):  Y[t, n]  = sum_k X[t, k]  * W[n, k]      (reference: csrc/mmq_core.cuh:211-267,
+//                                                                450-514, 573-635)
+//   backward (kBwd):  dX[t, k] = sum_n dY[t, n] * W[n, k]      (reference: csrc/ck/mmq_backward.cuh:496-1004,
+//                                                                csrc/ck/grouped_mmq_backward.cuh:42-152, 308-458)
+//
+// The weight side sits on the UMMA M axis (128 TMEM lanes = 128 out-features forward, 128
+// in-features backward) and the tokens on the UMMA N axis (16..256 TMEM columns), so a ragged
+// expert group costs at most 15 padded token columns and one decoded weight tile is reused by up
+// to 256 tokens.  Raw GGUF super-blocks are bulk-copied into shared memory, decoded there to bf16
+// in the 128-byte-swizzled operand layout by eight decode warps, and consumed by tcgen05.mma
+// (kind::f16, bf16 x bf16 -> fp32 in TMEM).  The same decoded image [weight row n][64 k] is a
+// K-major operand forward and an MN-major operand backward, so neither direction transposes.
+// The reduction order of every output element is fixed (ascending reduction index, 16 per UMMA),
+// independent of tiling, which makes grouped == dense and pair == two singles bit-exact.
+//
+// Warp roles (512 threads): 0 activation producer (TMA), 1 UMMA issuer + TMEM owner, 2 raw
+// weight producer (bulk copies), 3 idle, 4-11 decode, 12-15 epilogue (TMEM -> bf16 -> global).
+// All waits are bounded (ptx.cuh); a wait that gives up unwinds every role to the common exit,
+// which frees TMEM and records a status code.
+#pragma once
+
+#include "gguf_decode.cuh"
+#include "ptx.cuh"
+
+namespace tgo {
+
+enum : int { kFwd = 0, kBwd = 1 };
+
+constexpr int kTileM = 128;          // weight-side extent of one tile (TMEM lanes)
+constexpr int kTileTok = 256;        // most tokens per tile (TMEM columns of one accumulator)
+constexpr int kStepK = 64;           // reduction elements per pipeline step (one swizzle row)
+constexpr int kActTileBytes = kTileTok * 128;
+constexpr int kWgtTileBytes = kTileM * 128;
+constexpr int kActStages = 4;
+constexpr int kDecodeWarps = 8;
+constexpr int kGemmThreads = 512;
+constexpr int kTmemCols = 512;       // two accumulators of 256 columns
+constexpr int kNumBoxes = 5;         // activation TMA boxes of 256, 128, 64, 32, 16 rows
+constexpr int kSmemLimit = 232448;   // 227 KB opt-in limit per CTA
+
+struct ActMaps {
+    CUtensorMap box[kNumBoxes];
+};
+
+struct GemmArgs {
+    ActMaps act_maps[2];                 // per set: activations [rows][red] bf16, 128B swizzle
+    const __nv_bfloat16* act[2];         // same tensors, for the non-TMA loader
+    const uint8_t* wgt[2];               // packed weights [E][N][K/256 blocks]
+    __nv_bfloat16* out[2];
+    long long expert_bytes;              // N * (K/256) * block bytes
+    long long wgt_bytes;                 // E * expert_bytes
+    const int4* tasks;                   // (expert, first row, tokens, -) or null for dense
+    const int* task_count;               // device count of tasks (grouped)
+    int* status;                         // device status word (0 = ok)
+    const uint64_t* iq2s_grid;           // IQ2_S codebook (1024 entries) in global memory
+    int rows;                            // R
+    int out_features;                    // N
+    int in_features;                     // K
+    int nsets;                           // 1, or 2 for the gate/up pair
+    int num_experts;
+    int dense_tasks;                     // dense: number of token tiles
+    int dense_tok;                       // dense: tokens per tile (multiple of 16)
+    int use_tma;                         // 0: activation rows are not 16-byte multiples
+};
+
+template <int QT, int MODE>
+struct GemmCfg {
+    using Fmt = BlockFmt<QT>;
+    static constexpr int kRawRows = MODE == kFwd ? 128 : 64;    // block windows per raw stage
+    static constexpr int kRawStages = MODE == kFwd ? 2 : 4;
+    static constexpr int kRawStageBytes = kRawRows * Fmt::kSlot;
+    static constexpr int kRawBytes = kRawStages * kRawStageBytes;
+    static constexpr int kGridBytes = QT == QT_IQ2_S ? 8192 : 0;
+    static constexpr int kFixed = 1024 /*alignment slack*/ + 512 /*barriers etc.*/ +
+                                  kActStages * kActTileBytes + kRawBytes + kGridBytes;
+    static constexpr int kWgtStagesFit = (kSmemLimit - kFixed) / kWgtTileBytes;
+    static constexpr int kWgtStages = kWgtStagesFit >= 3 ? 3 : kWgtStagesFit;
+    static_assert(kWgtStages >= 2, "shared memory budget");
+    static constexpr int kSmemBytes = kFixed + kWgtStages * kWgtTileBytes;
+};
+
+struct TileInfo {
+    int expert, row0, ntok, ntok_pad, set, m0;
+};
+
+
+template <int MODE>
+__device__ __forceinline__ bool load_tile(const GemmArgs& a, int tile, int mtiles, int mtiles_set,
+                                          TileInfo& t) {
+    const int task = tile / mtiles;
+    const int mt = tile - task * mtiles;
+    if (a.tasks != nullptr) {
+        const int4 k = a.tasks[task];
+        t.expert = k.x;
+        t.row0 = k.y;
+        t.ntok = k.z;
+    } else {
+        t.expert = 0;
+        t.row0 = task * a.dense_tok;
+        t.ntok = min(a.dense_tok, a.rows - t.row0);
+    }
+    t.ntok_pad = (t.ntok + 15) & ~15;
+    if (MODE == kFwd) {
+        t.set = mt / mtiles_set;
+        t.m0 = (mt - t.set * mtiles_set) * kTileM;
+    } else {
+        t.set = 0;
+        t.m0 = mt * kTileM;
+    }
+    return t.ntok > 0;
+}
+
+// One lane waits, the whole warp learns the outcome (keeps the warp converged).
+__device__ __forceinline__ bool lane0_wait(uint32_t bar, uint32_t parity, volatile int* abort_word,
+                                           int code, int lane) {
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait(bar, parity, abort_word, code) ? 1 : 0;
+    return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+}
+// Every lane waits (each needs the acquire), the warp agrees on the outcome.
+__device__ __forceinline__ bool all_wait(uint32_t bar, uint32_t parity, volatile int* abort_word,
+                                         int code) {
+    const bool ok = mbar_wait(bar, parity, abort_word, code);
+    return __all_sync(0xFFFFFFFFu, ok) != 0;
+}
+
+template <int QT, int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
+    using Cfg = GemmCfg<QT, MODE>;
+    using Fmt = BlockFmt<QT>;
+    constexpr int NA = Cfg::kWgtStages, NB = kActStages, NR = Cfg::kRawStages;
+
+    extern __shared__ uint8_t smem_dyn[];
+    const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    uint8_t* smem = smem_dyn + (smem_base - smem_u32(smem_dyn));
+
+    // carve-up (all operand tiles 1024-byte aligned)
+    const uint32_t act_s = smem_base;
+    const uint32_t wgt_s = act_s + NB * kActTileBytes;
+    const uint32_t raw_s = wgt_s + NA * kWgtTileBytes;
+    uint8_t* act_g = smem;
+    uint8_t* wgt_g = act_g + NB * kActTileBytes;
+    uint8_t* raw_g = wgt_g + NA * kWgtTileBytes;
+    uint8_t* grid_g = raw_g + Cfg::kRawBytes;
+    uint8_t* misc_g = grid_g + Cfg::kGridBytes;
+    const uint32_t misc_s = raw_s + Cfg::kRawBytes + Cfg::kGridBytes;
+    // barriers (8 bytes each)
+    const uint32_t bar_act_full = misc_s;                    // NB
+    const uint32_t bar_act_empty = bar_act_full + 8 * NB;    // NB
+    const uint32_t bar_wgt_full = bar_act_empty + 8 * NB;    // NA
+    const uint32_t bar_wgt_empty = bar_wgt_full + 8 * NA;    // NA
+    const uint32_t bar_raw_full = bar_wgt_empty + 8 * NA;    // NR
+    const uint32_t bar_raw_empty = bar_raw_full + 8 * NR;    // NR
+    const uint32_t bar_acc_full = bar_raw_empty + 8 * NR;    // 2
+    const uint32_t bar_acc_empty = bar_acc_full + 16;        // 2
+    constexpr int kBarBytes = 8 * (2 * NB + 2 * NA + 2 * NR + 4);
+    static_assert(kBarBytes + 16 <= 512, "misc region");
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc_g + kBarBytes);
+    volatile int* abort_word = reinterpret_cast<volatile int*>(misc_g + kBarBytes + 4);
+    const uint64_t* grid = reinterpret_cast<const uint64_t*>(grid_g);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int N = args.out_features, K = args.in_features;
+    const int nkb = K >> 8;
+    // tile space
+    const int mtiles_set = MODE == kFwd ? (N + kTileM - 1) / kTileM : K / kTileM;
+    const int mtiles = MODE == kFwd ? mtiles_set * args.nsets : mtiles_set;
+    const int steps_set = MODE == kFwd ? K / kStepK : (N + kStepK - 1) / kStepK;
+    const int nsteps = MODE == kFwd ? steps_set : steps_set * args.nsets;
+    const int ntasks = args.tasks != nullptr ? *args.task_count : args.dense_tasks;
+    const long long total_tiles = static_cast<long long>(ntasks) * mtiles;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NB; ++i) { mbar_init(bar_act_full + 8 * i, 1); mbar_init(bar_act_empty + 8 * i, 1); }
+        for (int i = 0; i < NA; ++i) { mbar_init(bar_wgt_full + 8 * i, kDecodeWarps); mbar_init(bar_wgt_empty + 8 * i, 1); }
+        for (int i = 0; i < NR; ++i) { mbar_init(bar_raw_full + 8 * i, 1); mbar_init(bar_raw_empty + 8 * i, kDecodeWarps); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, 4); }
+        *abort_word = 0;
+        mbar_fence_init();
+    }
+    if (QT == QT_IQ2_S) {
+        uint64_t* gdst = reinterpret_cast<uint64_t*>(grid_g);
+        for (int i = threadIdx.x; i < 1024; i += kGemmThreads) gdst[i] = args.iq2s_grid[i];
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ activation producer
+        if (args.use_tma) {
+            if (lane == 0) {
+                for (int s = 0; s < args.nsets; ++s)
+                    for (int b = 0; b < kNumBoxes; ++b) prefetch_tmap(&args.act_maps[s].box[b]);
+            }
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                TileInfo t;
+                if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+                for (int step = 0; step < nsteps; ++step, ++it) {
+                    const uint32_t s = it % NB, ph = (it / NB) & 1u;
+                    if (!lane0_wait(bar_act_empty + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty, lane)) { ok = false; break; }
+                    if (lane == 0) {
+                        const int set = MODE == kFwd ? 0 : step / steps_set;
+                        const int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
+                        const uint32_t bar = bar_act_full + 8 * s;
+                        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(t.ntok_pad) * 128u);
+                        uint32_t dst = act_s + s * kActTileBytes;
+                        int row = t.row0, rem = t.ntok_pad;
+#pragma unroll
+                        for (int b = 0; b < kNumBoxes; ++b) {
+                            const int h = 256 >> b;
+                            if (rem >= h) {
+                                tma_load_2d(dst, &args.act_maps[set].box[b], bar, red0, row);
+                                dst += h * 128;
+                                row += h;
+                                rem -= h;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+        } else {
+            // Rows whose byte length is not a multiple of 16 cannot be described to TMA: copy
+            // with plain loads, zero-filling past the matrix edge, into the same swizzled image.
+            uint32_t it = 0;
+            bool ok = true;
+            const int red_total = MODE == kFwd ? K : N;
+            for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                TileInfo t;
+                if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+                for (int step = 0; step < nsteps; ++step, ++it) {
+                    const uint32_t s = it % NB, ph = (it / NB) & 1u;
+                    if (!lane0_wait(bar_act_empty + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty, lane)) { ok = false; break; }
+                    const int set = MODE == kFwd ? 0 : step / steps_set;
+                    const int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
+                    const __nv_bfloat16* src = args.act[set];
+                    uint8_t* dst = act_g + s * kActTileBytes;
+                    for (int idx = lane; idx < t.ntok_pad * 8; idx += 32) {
+                        const int r = idx >> 3, c = idx & 7;
+                        const long long grow = static_cast<long long>(t.row0) + r;
+                        alignas(16) __nv_bfloat16 v[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const int col = red0 + c * 8 + e;
+                            v[e] = (grow < args.rows && col < red_total) ? src[grow * red_total + col]
+                                                                         : __float2bfloat16(0.0f);
+                        }
+                        *reinterpret_cast<uint4*>(dst + r * 128 + ((c ^ (r & 7)) << 4)) =
+                            *reinterpret_cast<const uint4*>(v);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_act_full + 8 * s);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ UMMA issuer
+        uint32_t ita = 0, itb = 0, tl = 0;
+        bool ok = true;
+        for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            TileInfo t;
+            if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+            const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
+            ++tl;
+            if (!lane0_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kAbortAccEmpty, lane)) break;
+            tc_fence_after_sync();
+            const uint32_t d_tmem = tmem_base + acc * kTileTok;
+            const uint32_t idesc =
+                umma_idesc_bf16(static_cast<uint32_t>(t.ntok_pad), MODE == kBwd ? 1u : 0u, 0u);
+            for (int step = 0; step < nsteps; ++step, ++ita, ++itb) {
+                const uint32_t sa = ita % NA, pa = (ita / NA) & 1u;
+                const uint32_t sb = itb % NB, pb = (itb / NB) & 1u;
+                if (!lane0_wait(bar_wgt_full + 8 * sa, pa, abort_word, kAbortWgtFull, lane)) { ok = false; break; }
+                if (!lane0_wait(bar_act_full + 8 * sb, pb, abort_word, kAbortActFull, lane)) { ok = false; break; }
+                if (lane == 0) {
+                    tc_fence_after_sync();
+                    const uint32_t wa = wgt_s + sa * kWgtTileBytes;
+                    const uint32_t ba = act_s + sb * kActTileBytes;
+#pragma unroll
+                    for (int kk = 0; kk < kStepK / 16; ++kk) {
+                        const uint64_t adesc = MODE == kFwd ? umma_smem_desc(wa + kk * 32, 16, 1024)
+                                                            : umma_smem_desc(wa + kk * 2048, 8192, 1024);
+                        const uint64_t bdesc = umma_smem_desc(ba + kk * 32, 16, 1024);
+                        umma_bf16(d_tmem, adesc, bdesc, idesc, (step | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(bar_wgt_empty + 8 * sa);
+                    umma_commit(bar_act_empty + 8 * sb);
+                }
+                __syncwarp();
+            }
+            if (ok && lane == 0) umma_commit(bar_acc_full + 8 * acc);
+            __syncwarp();
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------ raw weight producer
+        uint32_t itr = 0;
+        bool ok = true;
+        constexpr int kRowsPerLane = Cfg::kRawRows / 32;
+        for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            TileInfo t;
+            if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+            const int nraw = MODE == kFwd ? nkb : nsteps;
+            for (int ri = 0; ri < nraw; ++ri, ++itr) {
+                const uint32_t r = itr % NR, ph = (itr / NR) & 1u;
+                if (!lane0_wait(bar_raw_empty + 8 * r, ph ^ 1u, abort_word, kAbortRawEmpty, lane)) { ok = false; break; }
+                int set, n_first, kb;
+                if (MODE == kFwd) {
+                    set = t.set; n_first = t.m0; kb = ri;
+                } else {
+                    set = ri / steps_set; n_first = (ri - set * steps_set) * kStepK; kb = t.m0 >> 8;
+                }
+                const uint8_t* wbase = args.wgt[set];
+                const long long ebase = static_cast<long long>(t.expert) * args.expert_bytes;
+                long long srcs[kRowsPerLane];
+                int nbulk = 0;
+#pragma unroll
+                for (int i = 0; i < kRowsPerLane; ++i) {
+                    const int row = lane + 32 * i;
+                    const int n = n_first + row;
+                    long long src = -1;  // -1: no row, otherwise aligned byte offset; bit 62 marks manual copy
+                    if (n < N) {
+                        const long long off = ebase + (static_cast<long long>(n) * nkb + kb) * Fmt::kBytes;
+                        src = off & ~15LL;
+                        if (src + Fmt::kCopy > args.wgt_bytes) src |= (1LL << 62);
+                    }
+                    srcs[i] = src;
+                    nbulk += __popc(__ballot_sync(0xFFFFFFFFu, src >= 0 && (src >> 62) == 0));
+                }
+                const uint32_t bar = bar_raw_full + 8 * r;
+                if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(nbulk) * Fmt::kCopy);
+                __syncwarp();
+                const uint32_t stage_s = raw_s + r * Cfg::kRawStageBytes;
+                uint8_t* stage_g = raw_g + r * Cfg::kRawStageBytes;
+#pragma unroll
+                for (int i = 0; i < kRowsPerLane; ++i) {
+                    const int row = lane + 32 * i;
+                    const long long src = srcs[i];
+                    if (src < 0) continue;
+                    if ((src >> 62) == 0) {
+                        bulk_load(stage_s + row * Fmt::kSlot, wbase + src, Fmt::kCopy, bar);
+                    } else {
+                        // last block(s) of the tensor: the 16-byte window would run past the end
+                        const long long s0 = src & ~(1LL << 62);
+                        const int nbytes = static_cast<int>(args.wgt_bytes - s0);  // even
+                        const uint16_t* g16 = reinterpret_cast<const uint16_t*>(wbase + s0);
+                        uint16_t* d16 = reinterpret_cast<uint16_t*>(stage_g + row * Fmt::kSlot);
+                        for (int b = 0; b < nbytes / 2; ++b) d16[b] = g16[b];
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar);
+            }
+        }
+    } else if (warp >= 4 && warp < 4 + kDecodeWarps) {
+        // ------------------------------------------------------------ decode warps
+        const int dt = threadIdx.x - 128;  // 0..255
+        uint32_t ita = 0, itr = 0;
+        bool ok = true;
+        for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            TileInfo t;
+            if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+            const long long ebase = static_cast<long long>(t.expert) * args.expert_bytes;
+            for (int step = 0; step < nsteps; ++step, ++ita) {
+                int row, g, n, kb;
+                uint32_t dst_off;  // byte offset of this thread's first chunk row inside the tile
+                int cbase;         // first 16-byte chunk index (0 or 4) in the 128-byte row
+                if (MODE == kFwd) {
+                    row = dt >> 1;
+                    const int half = dt & 1;
+                    kb = step >> 2;
+                    g = 2 * (step & 3) + half;
+                    n = t.m0 + row;
+                    dst_off = row * 128;
+                    cbase = 4 * half;
+                } else {
+                    row = dt >> 2;
+                    const int q = dt & 3;
+                    const int set = step / steps_set;
+                    kb = t.m0 >> 8;
+                    g = ((t.m0 >> 7) & 1) * 4 + q;
+                    n = (step - set * steps_set) * kStepK + row;
+                    dst_off = (q >> 1) * 8192 + row * 128;
+                    cbase = 4 * (q & 1);
+                }
+                const uint32_t r = itr % NR, rph = (itr / NR) & 1u;
+                const bool first_use = MODE == kFwd ? (step & 3) == 0 : true;
+                const bool last_use = MODE == kFwd ? (step & 3) == 3 : true;
+                if (first_use) {
+                    if (!all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull)) { ok = false; break; }
+                }
+                const uint32_t sa = ita % NA, pa = (ita / NA) & 1u;
+                if (!all_wait(bar_wgt_empty + 8 * sa, pa ^ 1u, abort_word, kAbortWgtEmpty)) { ok = false; break; }
+                uint4 o[4];
+                if (n < N) {
+                    int mis = 0;
+                    if (!Fmt::kAligned) {
+                        const long long off = ebase + (static_cast<long long>(n) * nkb + kb) * Fmt::kBytes;
+                        mis = static_cast<int>(off & 15);
+                    }
+                    const uint8_t* blk = raw_g + r * Cfg::kRawStageBytes + row * Fmt::kSlot + mis;
+                    decode32<QT>(blk, g, grid, o);
+                } else {
+                    o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
+                }
+                uint8_t* tile_g = wgt_g + sa * kWgtTileBytes + dst_off;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(tile_g + (((cbase + c) ^ (row & 7)) << 4)) = o[c];
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar_wgt_full + 8 * sa);
+                    if (last_use) mbar_arrive(bar_raw_empty + 8 * r);
+                }
+                if (last_use) ++itr;
+            }
+        }
+    } else if (warp >= 12) {
+        // ------------------------------------------------------------ epilogue
+        const int quad = warp & 3;
+        uint32_t tl = 0;
+        const int mdim = MODE == kFwd ? N : K;
+        for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            TileInfo t;
+            if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+            const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
+            ++tl;
+            if (!all_wait(bar_acc_full + 8 * acc, aph, abort_word, kAbortAccFull)) break;
+            tc_fence_after_sync();
+            const int m = t.m0 + quad * 32 + lane;
+            const bool m_ok = m < mdim;
+            __nv_bfloat16* out = args.out[MODE == kFwd ? t.set : 0] + static_cast<long long>(t.row0) * mdim + m;
+            const uint32_t taddr = tmem_base + acc * kTileTok + (static_cast<uint32_t>(quad * 32) << 16);
+            for (int c0 = 0; c0 < t.ntok_pad; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(taddr + c0, v);
+                tmem_ld_wait();
+                if (m_ok) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j < t.ntok)
+                            out[static_cast<long long>(c0 + j) * mdim] = __float2bfloat16(__uint_as_float(v[j]));
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+        }
+    }
+
+    // ------------------------------------------------------------ common exit
+    if (*abort_word != 0) {
+        // Some wait gave up.  Give copies and UMMAs still in flight a bounded time to land before
+        // shared memory and TMEM are released.
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_word != 0 && args.status != nullptr)
+        atomicCAS(args.status, 0, (*abort_word) | (static_cast<int>(blockIdx.x) << 8));
+}
+
+}  // namespace tgo

@@ -1,0 +1,435 @@
+// C-ABI entry points of libtgo_mmq.so (declared in include/tgo_mmq.h) plus the small kernels
+// that are not the GEMM itself: the tile-list builder and the stand-alone dequantiser.
+//
+// Host responsibilities mirrored from the reference's native layer (csrc/mmq_hip.cu): argument
+// validation on host-visible sizes only, launch on the caller's stream, launch-error check; no
+// host synchronisation and no device-to-host read on any path except tgo_device_status.
+#include "../../include/tgo_mmq.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include "mmq_launch.h"
+
+namespace tgo {
+
+// ------------------------------------------------------------------ device globals
+__device__ int g_status = 0;
+
+__device__ const uint64_t g_iq2s_grid[1024] = {
+#include "iq2s_grid.inc"
+};
+
+// ------------------------------------------------------------------ errors
+static thread_local std::string t_error;
+
+static int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    t_error = buf;
+    return code;
+}
+static int cuda_fail(cudaError_t e, const char* what) {
+    return fail(TGO_E_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int num_sms() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev < 64 && cached[dev] > 0) return cached[dev];
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    if (dev < 64) cached[dev] = n;
+    return n;
+}
+
+static int* status_ptr() {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status) != cudaSuccess) return nullptr;
+    return p;
+}
+static const uint64_t* grid_ptr() {
+    const uint64_t* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(const_cast<uint64_t**>(&p)), g_iq2s_grid) != cudaSuccess)
+        return nullptr;
+    return p;
+}
+
+// ------------------------------------------------------------------ tensor maps
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    }
+    return fn;
+}
+
+// bf16 matrix [rows][inner], row-major; boxes of 64 columns x {256,128,64,32,16} rows with the
+// 128-byte swizzle.  Out-of-range rows / columns read as zero.
+static int make_act_maps(ActMaps& maps, const void* base, int64_t rows, int64_t inner) {
+    auto encode = encode_fn();
+    if (encode == nullptr) return fail(TGO_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(inner) * 2};
+    const cuuint32_t estride[2] = {1, 1};
+    for (int b = 0; b < kNumBoxes; ++b) {
+        const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(256 >> b)};
+        const CUresult r = encode(&maps.box[b], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim,
+                                  gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(TGO_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    }
+    return TGO_OK;
+}
+
+// ------------------------------------------------------------------ tile-list builder
+// Workspace layout: int32 count at byte 0, int4 tasks from byte 16.
+// One CTA: per group, the number of token tiles ceil(rows / 256); exclusive prefix sum; each
+// group then writes its tiles, split evenly and rounded up to 16 tokens.
+__global__ void __launch_bounds__(256) build_tiles_kernel(const int64_t* __restrict__ experts,
+                                                          const int32_t* __restrict__ offsets, int num_groups,
+                                                          int num_experts, int rows, int4* __restrict__ tasks,
+                                                          int* __restrict__ count, int capacity) {
+    __shared__ int warp_sums[8];
+    __shared__ int chunk_total;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int base = 0;
+    for (int g0 = 0; g0 < num_groups; g0 += 256) {
+        const int g = g0 + tid;
+        int nt = 0, beg = 0, end = 0;
+        long long e = -1;
+        if (g < num_groups) {
+            e = experts[g];
+            end = offsets[g];
+            beg = g > 0 ? offsets[g - 1] : 0;
+            const bool valid = e >= 0 && e < num_experts && beg >= 0 && beg < end && end <= rows;
+            if (valid) nt = (end - beg + kTileTok - 1) / kTileTok;
+        }
+        int incl = nt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += v;
+        }
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = lane < 8 ? warp_sums[lane] : 0;
+#pragma unroll
+            for (int d = 1; d < 8; d <<= 1) {
+                const int v = __shfl_up_sync(0xFFFFFFFFu, w, d);
+                if (lane >= d) w += v;
+            }
+            if (lane < 8) warp_sums[lane] = w;
+            if (lane == 7) chunk_total = w;
+        }
+        __syncthreads();
+        const int pos = base + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - nt;
+        if (nt > 0) {
+            const int n = end - beg;
+            const int per = (((n + nt - 1) / nt) + 15) & ~15;
+            for (int j = 0; j < nt; ++j) {
+                const int r0 = beg + j * per;
+                const int cnt = min(per, end - r0);
+                if (pos + j < capacity && cnt > 0) tasks[pos + j] = make_int4(static_cast<int>(e), r0, cnt, g);
+                else if (pos + j < capacity) tasks[pos + j] = make_int4(0, 0, 0, g);
+            }
+        }
+        base += chunk_total;
+        __syncthreads();
+    }
+    if (tid == 0) *count = min(base, capacity);
+}
+
+static int64_t task_capacity(int64_t rows, int64_t groups) { return rows / kTileTok + groups; }
+
+// ------------------------------------------------------------------ stand-alone dequantiser
+// 32 blocks per CTA: their 16-byte-aligned windows are copied into shared memory exactly as the
+// GEMM's raw-weight producer stages them, then decoded with the same decode32<>.
+template <int QT>
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ packed, long long n_blocks,
+                                                      long long total_bytes, const uint64_t* __restrict__ grid_g,
+                                                      __nv_bfloat16* __restrict__ out) {
+    using Fmt = BlockFmt<QT>;
+    __shared__ __align__(16) uint8_t windows[32 * Fmt::kSlot];
+    __shared__ uint64_t grid_s[QT == QT_IQ2_S ? 1024 : 1];
+    if (QT == QT_IQ2_S)
+        for (int i = threadIdx.x; i < 1024; i += 256) grid_s[i] = grid_g[i];
+    const long long b0 = static_cast<long long>(blockIdx.x) * 32;
+    constexpr int kChunks = Fmt::kCopy / 16;
+    for (int i = threadIdx.x; i < 32 * kChunks; i += 256) {
+        const int b = i / kChunks, c = i - b * kChunks;
+        const long long blk = b0 + b;
+        if (blk >= n_blocks) continue;
+        const long long src = ((blk * Fmt::kBytes) & ~15LL) + c * 16;
+        uint8_t* dst = windows + b * Fmt::kSlot + c * 16;
+        if (src + 16 <= total_bytes) {
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(packed + src);
+        } else {
+            for (int j = 0; j < 16 && src + j + 2 <= total_bytes; j += 2)
+                *reinterpret_cast<uint16_t*>(dst + j) = *reinterpret_cast<const uint16_t*>(packed + src + j);
+        }
+    }
+    __syncthreads();
+    const int b = threadIdx.x >> 3, g = threadIdx.x & 7;
+    const long long blk = b0 + b;
+    if (blk >= n_blocks) return;
+    const int mis = static_cast<int>((blk * Fmt::kBytes) & 15);
+    uint4 o[4];
+    decode32<QT>(windows + b * Fmt::kSlot + mis, g, grid_s, o);
+    uint4* dst = reinterpret_cast<uint4*>(out + blk * 256 + g * 32);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) dst[c] = o[c];
+}
+
+// ------------------------------------------------------------------ GEMM dispatch
+static int dispatch_gemm(int qt, int mode, const GemmArgs& args, int grid, cudaStream_t stream) {
+    int e;
+    switch (qt) {
+        case QT_Q3_K: e = launch_gemm_11(mode, args, grid, stream); break;
+        case QT_Q4_K: e = launch_gemm_12(mode, args, grid, stream); break;
+        case QT_Q5_K: e = launch_gemm_13(mode, args, grid, stream); break;
+        case QT_Q6_K: e = launch_gemm_14(mode, args, grid, stream); break;
+        case QT_IQ2_S: e = launch_gemm_22(mode, args, grid, stream); break;
+        default: return fail(TGO_E_ARG, "unsupported quant_type: %d", qt);
+    }
+    if (e != 0) return cuda_fail(static_cast<cudaError_t>(e), "mmq_gemm_kernel launch");
+    return TGO_OK;
+}
+
+struct Problem {
+    const void* act[2];
+    const void* wgt[2];
+    void* out[2];
+    int nsets;
+    int64_t rows, N, K, E;
+    int qt, mode;
+    const int64_t* experts;   // null: dense
+    const int32_t* offsets;
+    int64_t groups;
+    void* ws;
+    int64_t ws_bytes;
+};
+
+static int check_common(const Problem& p) {
+    const int64_t bb = tgo_block_bytes(p.qt);
+    if (bb < 0) return fail(TGO_E_ARG, "unsupported quant_type: %d", p.qt);
+    if (p.rows <= 0) return fail(TGO_E_ARG, "zero-row inputs are not supported");
+    if (p.K <= 0 || p.K % 256 != 0) return fail(TGO_E_ARG, "in_features must be a positive multiple of 256; got %lld", (long long)p.K);
+    if (p.N <= 0) return fail(TGO_E_ARG, "out_features must be positive; got %lld", (long long)p.N);
+    if (p.rows > INT32_MAX || p.N > INT32_MAX || p.K > INT32_MAX || p.E > INT32_MAX || p.groups > INT32_MAX)
+        return fail(TGO_E_ARG, "a dimension exceeds the kernel limit of 2^31-1");
+    const int nacts = p.mode == kFwd ? 1 : p.nsets;
+    for (int s = 0; s < nacts; ++s) {
+        if (p.act[s] == nullptr) return fail(TGO_E_ARG, "null tensor pointer");
+        if (!aligned16(p.act[s])) return fail(TGO_E_ARG, "activation data pointer must be 16-byte aligned");
+    }
+    for (int s = 0; s < p.nsets; ++s) {
+        if (p.wgt[s] == nullptr) return fail(TGO_E_ARG, "null tensor pointer");
+        if (!aligned16(p.wgt[s])) return fail(TGO_E_ARG, "packed_weight data pointer must be 16-byte aligned");
+    }
+    const int nouts = p.mode == kFwd ? p.nsets : 1;
+    for (int s = 0; s < nouts; ++s) {
+        if (p.out[s] == nullptr) return fail(TGO_E_ARG, "null output pointer");
+        if (!aligned16(p.out[s])) return fail(TGO_E_ARG, "output data pointer must be 16-byte aligned");
+    }
+    return TGO_OK;
+}
+
+static int run_problem(const Problem& p, cudaStream_t stream) {
+    int rc = check_common(p);
+    if (rc != TGO_OK) return rc;
+    GemmArgs a;
+    memset(&a, 0, sizeof(a));
+    const int64_t red = p.mode == kFwd ? p.K : p.N;  // activation row length
+    a.use_tma = (red * 2) % 16 == 0 ? 1 : 0;
+    const int nact = p.mode == kFwd ? 1 : p.nsets;
+    for (int s = 0; s < 2; ++s) {
+        const int src = s < nact ? s : 0;
+        a.act[s] = static_cast<const __nv_bfloat16*>(p.act[src]);
+        if (a.use_tma) {
+            rc = make_act_maps(a.act_maps[s], p.act[src], p.rows, red);
+            if (rc != TGO_OK) return rc;
+        }
+        a.wgt[s] = static_cast<const uint8_t*>(p.wgt[s < p.nsets ? s : 0]);
+        a.out[s] = static_cast<__nv_bfloat16*>(p.out[(p.mode == kFwd && s < p.nsets) ? s : 0]);
+    }
+    const int64_t bb = tgo_block_bytes(p.qt);
+    a.expert_bytes = p.N * (p.K / 256) * bb;
+    a.wgt_bytes = a.expert_bytes * p.E;
+    a.status = status_ptr();
+    a.iq2s_grid = grid_ptr();
+    if (a.status == nullptr || a.iq2s_grid == nullptr) return fail(TGO_E_CUDA, "cudaGetSymbolAddress failed");
+    a.rows = static_cast<int>(p.rows);
+    a.out_features = static_cast<int>(p.N);
+    a.in_features = static_cast<int>(p.K);
+    a.nsets = p.nsets;
+    a.num_experts = static_cast<int>(p.E);
+
+    const int64_t mtiles = p.mode == kFwd ? ((p.N + kTileM - 1) / kTileM) * p.nsets : p.K / kTileM;
+    int64_t max_tasks;
+    if (p.experts == nullptr) {
+        a.dense_tasks = static_cast<int>((p.rows + kTileTok - 1) / kTileTok);
+        a.dense_tok = static_cast<int>((((p.rows + a.dense_tasks - 1) / a.dense_tasks) + 15) & ~15LL);
+        max_tasks = a.dense_tasks;
+    } else {
+        const int64_t cap = task_capacity(p.rows, p.groups);
+        const int64_t need = tgo_grouped_workspace_bytes(p.rows, p.groups);
+        if (p.ws == nullptr || p.ws_bytes < need)
+            return fail(TGO_E_WORKSPACE, "workspace has %lld bytes, need %lld", (long long)p.ws_bytes, (long long)need);
+        if (!aligned16(p.ws)) return fail(TGO_E_ARG, "workspace pointer must be 16-byte aligned");
+        rc = tgo_build_tiles(p.experts, p.offsets, p.groups, p.E, p.rows, p.ws, p.ws_bytes, stream);
+        if (rc != TGO_OK) return rc;
+        a.task_count = static_cast<const int*>(p.ws);
+        a.tasks = reinterpret_cast<const int4*>(static_cast<const uint8_t*>(p.ws) + 16);
+        max_tasks = cap;
+    }
+    int64_t grid = max_tasks * mtiles;
+    if (grid > num_sms()) grid = num_sms();
+    if (grid < 1) grid = 1;
+    return dispatch_gemm(p.qt, p.mode, a, static_cast<int>(grid), stream);
+}
+
+}  // namespace tgo
+
+// ====================================================================== C ABI
+using namespace tgo;
+
+extern "C" {
+
+int tgo_version(void) { return 100; }
+
+const char* tgo_last_error(void) { return t_error.c_str(); }
+
+int64_t tgo_block_bytes(int quant_type) { return block_bytes_of(quant_type); }
+
+int tgo_device_status(int* status) {
+    if (status == nullptr) return fail(TGO_E_ARG, "null status pointer");
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_status, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyFromSymbol");
+    if (v != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyToSymbol");
+    }
+    *status = v;
+    return TGO_OK;
+}
+
+int tgo_dequantize_bf16(const void* packed, int64_t n_blocks, int quant_type, void* out_bf16, void* stream) {
+    const int64_t bb = tgo_block_bytes(quant_type);
+    if (bb < 0) return fail(TGO_E_ARG, "unsupported quant_type: %d", quant_type);
+    if (n_blocks <= 0) return fail(TGO_E_ARG, "n_blocks must be positive");
+    if (packed == nullptr || out_bf16 == nullptr) return fail(TGO_E_ARG, "null tensor pointer");
+    if (!aligned16(packed) || !aligned16(out_bf16)) return fail(TGO_E_ARG, "data pointers must be 16-byte aligned");
+    const uint64_t* grid = grid_ptr();
+    if (grid == nullptr) return fail(TGO_E_CUDA, "cudaGetSymbolAddress failed");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned nb = static_cast<unsigned>((n_blocks + 31) / 32);
+    const uint8_t* p = static_cast<const uint8_t*>(packed);
+    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out_bf16);
+    const long long total = n_blocks * bb;
+    switch (quant_type) {
+        case QT_Q3_K: dequant_kernel<QT_Q3_K><<<nb, 256, 0, s>>>(p, n_blocks, total, grid, o); break;
+        case QT_Q4_K: dequant_kernel<QT_Q4_K><<<nb, 256, 0, s>>>(p, n_blocks, total, grid, o); break;
+        case QT_Q5_K: dequant_kernel<QT_Q5_K><<<nb, 256, 0, s>>>(p, n_blocks, total, grid, o); break;
+        case QT_Q6_K: dequant_kernel<QT_Q6_K><<<nb, 256, 0, s>>>(p, n_blocks, total, grid, o); break;
+        default: dequant_kernel<QT_IQ2_S><<<nb, 256, 0, s>>>(p, n_blocks, total, grid, o); break;
+    }
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "dequant_kernel launch");
+    return TGO_OK;
+}
+
+int tgo_mmq_fwd(const void* x, const void* packed_weight, void* y, int64_t rows, int64_t out_features,
+                int64_t in_features, int quant_type, void* stream) {
+    Problem p = {};
+    p.act[0] = x; p.wgt[0] = packed_weight; p.out[0] = y; p.nsets = 1;
+    p.rows = rows; p.N = out_features; p.K = in_features; p.E = 1; p.qt = quant_type; p.mode = kFwd;
+    return run_problem(p, static_cast<cudaStream_t>(stream));
+}
+
+int tgo_mmq_dx(const void* dy, const void* packed_weight, void* dx, int64_t rows, int64_t out_features,
+               int64_t in_features, int quant_type, void* stream) {
+    Problem p = {};
+    p.act[0] = dy; p.wgt[0] = packed_weight; p.out[0] = dx; p.nsets = 1;
+    p.rows = rows; p.N = out_features; p.K = in_features; p.E = 1; p.qt = quant_type; p.mode = kBwd;
+    return run_problem(p, static_cast<cudaStream_t>(stream));
+}
+
+int64_t tgo_grouped_workspace_bytes(int64_t rows, int64_t num_groups) {
+    if (rows < 0 || num_groups < 0) return -1;
+    return 16 + 16 * task_capacity(rows, num_groups);
+}
+
+int tgo_build_tiles(const int64_t* expert_indices, const int32_t* expert_offsets, int64_t num_groups,
+                    int64_t num_experts, int64_t rows, void* workspace, int64_t workspace_bytes, void* stream) {
+    if (expert_indices == nullptr || expert_offsets == nullptr || workspace == nullptr)
+        return fail(TGO_E_ARG, "null pointer");
+    if (num_groups <= 0) return fail(TGO_E_ARG, "grouped MMQ requires at least one active expert");
+    if (num_experts <= 0) return fail(TGO_E_ARG, "packed_weight must contain at least one expert");
+    if (rows <= 0) return fail(TGO_E_ARG, "zero-row inputs are not supported");
+    if (rows > INT32_MAX || num_groups > INT32_MAX || num_experts > INT32_MAX)
+        return fail(TGO_E_ARG, "a dimension exceeds the kernel limit of 2^31-1");
+    const int64_t need = tgo_grouped_workspace_bytes(rows, num_groups);
+    if (workspace_bytes < need)
+        return fail(TGO_E_WORKSPACE, "workspace has %lld bytes, need %lld", (long long)workspace_bytes, (long long)need);
+    if (!aligned16(workspace)) return fail(TGO_E_ARG, "workspace pointer must be 16-byte aligned");
+    int* count = static_cast<int*>(workspace);
+    int4* tasks = reinterpret_cast<int4*>(static_cast<uint8_t*>(workspace) + 16);
+    build_tiles_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        expert_indices, expert_offsets, static_cast<int>(num_groups), static_cast<int>(num_experts),
+        static_cast<int>(rows), tasks, count, static_cast<int>(task_capacity(rows, num_groups)));
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "build_tiles_kernel launch");
+    return TGO_OK;
+}
+
+int tgo_grouped_fwd(const void* x, const void* w0, const void* w1, void* y0, void* y1,
+                    const int64_t* expert_indices, const int32_t* expert_offsets, int64_t num_groups,
+                    int64_t num_experts, int64_t rows, int64_t out_features, int64_t in_features, int quant_type,
+                    void* workspace, int64_t workspace_bytes, void* stream) {
+    if ((w1 == nullptr) != (y1 == nullptr)) return fail(TGO_E_ARG, "w1 and y1 must both be given or both be null");
+    if (expert_indices == nullptr || expert_offsets == nullptr) return fail(TGO_E_ARG, "null routing pointer");
+    if (num_groups > num_experts) return fail(TGO_E_ARG, "active expert count exceeds packed expert count");
+    Problem p = {};
+    p.act[0] = x; p.wgt[0] = w0; p.wgt[1] = w1; p.out[0] = y0; p.out[1] = y1; p.nsets = w1 ? 2 : 1;
+    p.rows = rows; p.N = out_features; p.K = in_features; p.E = num_experts; p.qt = quant_type; p.mode = kFwd;
+    p.experts = expert_indices; p.offsets = expert_offsets; p.groups = num_groups;
+    p.ws = workspace; p.ws_bytes = workspace_bytes;
+    return run_problem(p, static_cast<cudaStream_t>(stream));
+}
+
+int tgo_grouped_dx(const void* dy0, const void* dy1, const void* w0, const void* w1, void* dx,
+                   const int64_t* expert_indices, const int32_t* expert_offsets, int64_t num_groups,
+                   int64_t num_experts, int64_t rows, int64_t out_features, int64_t in_features, int quant_type,
+                   void* workspace, int64_t workspace_bytes, void* stream) {
+    if ((w1 == nullptr) != (dy1 == nullptr)) return fail(TGO_E_ARG, "w1 and dy1 must both be given or both be null");
+    if (expert_indices == nullptr || expert_offsets == nullptr) return fail(TGO_E_ARG, "null routing pointer");
+    if (num_groups > num_experts) return fail(TGO_E_ARG, "active expert count exceeds packed expert count");
+    Problem p = {};
+    p.act[0] = dy0; p.act[1] = dy1; p.wgt[0] = w0; p.wgt[1] = w1; p.out[0] = dx; p.nsets = w1 ? 2 : 1;
+    p.rows = rows; p.N = out_features; p.K = in_features; p.E = num_experts; p.qt = quant_type; p.mode = kBwd;
+    p.experts = expert_indices; p.offsets = expert_offsets; p.groups = num_groups;
+    p.ws = workspace; p.ws_bytes = workspace_bytes;
+    return run_problem(p, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
