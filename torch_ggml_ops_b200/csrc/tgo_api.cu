@@ -255,6 +255,12 @@ static int check_common(const Problem& p) {
 static int run_problem(const Problem& p, cudaStream_t stream) {
     int rc = check_common(p);
     if (rc != TGO_OK) return rc;
+    if (p.experts != nullptr) {
+        const int64_t need = tgo_grouped_workspace_bytes(p.rows, p.groups);
+        if (p.ws == nullptr || p.ws_bytes < need)
+            return fail(TGO_E_WORKSPACE, "workspace has %lld bytes, need %lld", (long long)p.ws_bytes, (long long)need);
+        if (!aligned16(p.ws)) return fail(TGO_E_ARG, "workspace pointer must be 16-byte aligned");
+    }
     GemmArgs a;
     memset(&a, 0, sizeof(a));
     const int64_t red = p.mode == kFwd ? p.K : p.N;  // activation row length
@@ -290,10 +296,6 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
         max_tasks = a.dense_tasks;
     } else {
         const int64_t cap = task_capacity(p.rows, p.groups);
-        const int64_t need = tgo_grouped_workspace_bytes(p.rows, p.groups);
-        if (p.ws == nullptr || p.ws_bytes < need)
-            return fail(TGO_E_WORKSPACE, "workspace has %lld bytes, need %lld", (long long)p.ws_bytes, (long long)need);
-        if (!aligned16(p.ws)) return fail(TGO_E_ARG, "workspace pointer must be 16-byte aligned");
         rc = tgo_build_tiles(p.experts, p.offsets, p.groups, p.E, p.rows, p.ws, p.ws_bytes, stream);
         if (rc != TGO_OK) return rc;
         a.task_count = static_cast<const int*>(p.ws);
