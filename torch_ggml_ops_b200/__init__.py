@@ -13,7 +13,7 @@ try:
 except ImportError as exc:  # pragma: no cover - build problem, not a runtime path
     raise ImportError(
         "torch_ggml_ops_b200: the native module is missing or failed to load "
-        f"({exc}). Build it with `python -m torch_ggml_ops_b200._build`; there is no fallback path."
+        f"({exc}). Build it with `python torch_ggml_ops_b200/_build.py`; there is no fallback path."
     ) from exc
 
 from . import native  # noqa: E402,F401  ctypes view of the same C ABI (tests, benchmarks)

@@ -12,7 +12,8 @@ The IQ2_S codebook is not kept in the source tree: it is written to ``build/iq2s
 the installed ``gguf`` package (the same table the reference vendors at
 csrc/vendor/llama_cpp/iq2_s_grid.cuh:7-263) and its SHA-256 is asserted.
 
-Run as ``python -m torch_ggml_ops_b200._build`` or call :func:`build`.
+Run as ``python torch_ggml_ops_b200/_build.py`` (a plain script: the package itself cannot be
+imported before its native module exists) or load this file and call :func:`build`.
 """
 from __future__ import annotations
 
@@ -41,6 +42,14 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 def _nvcc() -> str:
     cand = os.environ.get("NVCC") or "/usr/local/cuda/bin/nvcc"
     return cand if Path(cand).exists() else "nvcc"
+
+
+def _host_cxx() -> str:
+    """Host C++ compiler for the stable-ABI module.  The distribution compiler is preferred over
+    whatever is first on PATH because it is the one whose shared libstdc++ is installed."""
+    if os.environ.get("TGO_CXX"):
+        return os.environ["TGO_CXX"]
+    return "/usr/bin/g++" if Path("/usr/bin/g++").exists() else "g++"
 
 
 def _newer(target: Path, sources) -> bool:
@@ -91,7 +100,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(job):
         src, obj, flags = job
-        cmd = [_nvcc(), *NVCC_FLAGS, *flags, "-I", str(BUILD), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        cmd = [_nvcc(), "-ccbin", _host_cxx(), *NVCC_FLAGS, *flags, "-I", str(BUILD), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         _run(cmd)
@@ -101,7 +110,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
             list(ex.map(compile_one, todo))
     objs = [o for (_, o, _) in jobs]
     if force or todo or not _newer(LIB_PATH, objs):
-        _run([_nvcc(), "-shared", "-cudart", "shared", "-o", str(LIB_PATH), *map(str, objs),
+        _run([_nvcc(), "-ccbin", _host_cxx(), "-shared", "-cudart", "shared", "-o", str(LIB_PATH), *map(str, objs),
               "-Xlinker", "-rpath,/usr/local/cuda/lib64"])
     return LIB_PATH
 
@@ -115,12 +124,18 @@ def build_shim(force: bool = False) -> Path:
     tdir = Path(torch.__file__).resolve().parent
     inc = [tdir / "include", tdir / "include" / "torch" / "csrc" / "api" / "include",
            Path(sysconfig.get_paths()["include"])]
-    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared",
+    cmd = [_host_cxx(), "-O2", "-std=c++17", "-fPIC", "-shared",
            "-DTORCH_TARGET_VERSION=0x020A000000000000", "-DTORCH_STABLE_ONLY", "-DUSE_CUDA", "-DPy_LIMITED_API=0x030A0000",
            *[f"-I{p}" for p in inc], str(src), "-o", str(SHIM_PATH),
            f"-L{LIB_DIR}", "-ltgo_mmq", f"-L{tdir / 'lib'}", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10",
            "-Wl,-rpath,$ORIGIN/lib", f"-Wl,-rpath,{tdir / 'lib'}"]
     _run(cmd)
+    # The module must use the process-wide shared libstdc++ (the one libtorch uses): a toolchain
+    # that silently links libstdc++.a gives it private iostream state and crashes in operator<<.
+    syms = subprocess.run(["nm", "-D", "--defined-only", str(SHIM_PATH)], capture_output=True, text=True).stdout
+    if "_ZNSo9_M_insertIlEERSoT_" in syms:
+        raise RuntimeError("the stable-ABI module was linked against a static libstdc++; set TGO_CXX to a g++ "
+                           "whose libstdc++.so is installed")
     return SHIM_PATH
 
 

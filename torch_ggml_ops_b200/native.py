@@ -37,7 +37,7 @@ def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
         if not _LIB_PATH.exists():
-            raise ImportError(f"{_LIB_PATH} is missing: run `python -m torch_ggml_ops_b200._build`")
+            raise ImportError(f"{_LIB_PATH} is missing: run `python torch_ggml_ops_b200/_build.py`")
         import torch  # noqa: F401  loads libcudart.so.12 into the process first
 
         handle = ctypes.CDLL(str(_LIB_PATH))
