@@ -83,6 +83,12 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 // bf16 matrix [rows][inner], row-major; boxes of 64 columns x {256,128,64,32,16} rows with the
 // 128-byte swizzle.  Out-of-range rows / columns read as zero.
 static int make_act_maps(ActMaps& maps, const void* base, int64_t rows, int64_t inner) {
+    // The encoder is a driver entry point and needs a context bound to the calling thread; a
+    // thread that has only inherited its device (an autograd worker, say) may not have one yet.
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce == cudaSuccess) ce = cudaSetDevice(dev);
+    if (ce != cudaSuccess) return cuda_fail(ce, "cudaSetDevice");
     auto encode = encode_fn();
     if (encode == nullptr) return fail(TGO_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows)};
