@@ -236,9 +236,16 @@ def gpu_arm(args):
             native.grouped_fwd(x_rows, w, None, y, None, ei, eo, EL, R, N, K, qt, ws)
             native.grouped_dx(dy_sorted, None, w, None, dx, ei, eo, EL, R, N, K, qt, ws)
 
-        for _ in range(max(args.warmup, 3)):
+        for _ in range(args.warmup if args.profile else max(args.warmup, 3)):
             step_resident()
         barrier()
+        if args.profile:
+            # minimal launch sequence for a profiler: no clock sampling, no end-to-end leg
+            for _ in range(args.steps):
+                step_resident()
+            barrier()
+            print(json.dumps({"profile": True, "steps": args.steps, "device_status": native.device_status()}))
+            return
         sampler = ClockSampler(local_rank)
         sampler.start()
         keep_busy_for(1.0, step_resident)
@@ -420,6 +427,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="single GPU only: run warm-up + steps of the device-resident step and exit (for ncu)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
