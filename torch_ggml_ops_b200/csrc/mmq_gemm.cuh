@@ -9,7 +9,7 @@
 // The weight side sits on the UMMA M axis (128 TMEM lanes = 128 out-features forward, 128
 // in-features backward) and the tokens on the UMMA N axis (16..256 TMEM columns), so a ragged
 // expert group costs at most 15 padded token columns and one decoded weight tile is reused by up
-// to 256 tokens.  Raw GGUF super-blocks are bulk-copied into shared memory, decoded there to bf16
+// to 256 tokens.  Raw GGUF super-blocks are staged into shared memory by TMA, decoded there to bf16
 // in the 128-byte-swizzled operand layout by eight decode warps, and consumed by tcgen05.mma
 // (kind::f16, bf16 x bf16 -> fp32 in TMEM).  The same decoded image [weight row n][64 k] is a
 // K-major operand forward and an MN-major operand backward, so neither direction transposes.
@@ -45,8 +45,19 @@ struct ActMaps {
     CUtensorMap box[kNumBoxes];
 };
 
+// Packed weights as 2-D byte tensors for TMA.  Rows of 110 / 210 / 82-byte blocks start on 2-byte
+// boundaries only, but the alignment of row g repeats with period P = 16 / gcd(row_bytes, 16)
+// (at most 8): rows g = r (mod P) are mutually 16-byte aligned.  Map r therefore describes the
+// rows of class r with row pitch P * row_bytes, based at the 16-byte boundary below row r, so a
+// tile of 128 (or 64) weight rows is fetched with P box loads of rows / P rows each.
+constexpr int kMaxWgtClasses = 8;
+struct WgtMaps {
+    CUtensorMap cls[kMaxWgtClasses];
+};
+
 struct GemmArgs {
     ActMaps act_maps[2];                 // per set: activations [rows][red] bf16, 128B swizzle
+    WgtMaps wgt_maps[2];                 // per set: packed weight rows by alignment class
     const __nv_bfloat16* act[2];         // same tensors, for the non-TMA loader
     const uint8_t* wgt[2];               // packed weights [E][N][K/256 blocks]
     __nv_bfloat16* out[2];
@@ -64,6 +75,9 @@ struct GemmArgs {
     int dense_tasks;                     // dense: number of token tiles
     int dense_tok;                       // dense: tokens per tile (multiple of 16)
     int use_tma;                         // 0: activation rows are not 16-byte multiples
+    int wgt_classes;                     // P: alignment classes of the packed weight rows (1, 2, 4 or 8)
+    int wgt_classes_log2;
+    int wgt_row_bytes;                   // (K / 256) * block bytes
 };
 
 template <int QT, int MODE>
@@ -71,10 +85,10 @@ struct GemmCfg {
     using Fmt = BlockFmt<QT>;
     static constexpr int kRawRows = MODE == kFwd ? 128 : 64;    // block windows per raw stage
     static constexpr int kRawStages = MODE == kFwd ? 2 : 4;
-    static constexpr int kRawStageBytes = kRawRows * Fmt::kSlot;
+    static constexpr int kRawStageBytes = kRawRows * Fmt::kCopy;
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kGridBytes = QT == QT_IQ2_S ? 8192 : 0;
-    static constexpr int kFixed = 1024 /*alignment slack*/ + 512 /*barriers etc.*/ +
+    static constexpr int kFixed = 1024 /*alignment slack*/ + 512 /*barriers etc.*/ + 128 /*read slack*/ +
                                   kActStages * kActTileBytes + kRawBytes + kGridBytes;
     static constexpr int kWgtStagesFit = (kSmemLimit - kFixed) / kWgtTileBytes;
     static constexpr int kWgtStages = kWgtStagesFit >= 3 ? 3 : kWgtStagesFit;
@@ -145,9 +159,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     uint8_t* act_g = smem;
     uint8_t* wgt_g = act_g + NB * kActTileBytes;
     uint8_t* raw_g = wgt_g + NA * kWgtTileBytes;
-    uint8_t* grid_g = raw_g + Cfg::kRawBytes;
+    uint8_t* grid_g = raw_g + Cfg::kRawBytes + 128;
     uint8_t* misc_g = grid_g + Cfg::kGridBytes;
-    const uint32_t misc_s = raw_s + Cfg::kRawBytes + Cfg::kGridBytes;
+    const uint32_t misc_s = raw_s + Cfg::kRawBytes + 128 + Cfg::kGridBytes;
     // barriers (8 bytes each)
     const uint32_t bar_act_full = misc_s;                    // NB
     const uint32_t bar_act_empty = bar_act_full + 8 * NB;    // NB
@@ -308,9 +322,15 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------ raw weight producer
+        // One box load per alignment class and stage: rows / P block windows of kCopy bytes each.
         uint32_t itr = 0;
         bool ok = true;
-        constexpr int kRowsPerLane = Cfg::kRawRows / 32;
+        const int P = args.wgt_classes, lgP = args.wgt_classes_log2;
+        constexpr int kRows = Cfg::kRawRows;
+        if (lane == 0) {
+            for (int s = 0; s < args.nsets; ++s)
+                for (int c = 0; c < P; ++c) prefetch_tmap(&args.wgt_maps[s].cls[c]);
+        }
         for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
             TileInfo t;
             if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
@@ -318,52 +338,27 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             for (int ri = 0; ri < nraw; ++ri, ++itr) {
                 const uint32_t r = itr % NR, ph = (itr / NR) & 1u;
                 if (!lane0_wait(bar_raw_empty + 8 * r, ph ^ 1u, abort_word, kAbortRawEmpty, lane)) { ok = false; break; }
-                int set, n_first, kb;
-                if (MODE == kFwd) {
-                    set = t.set; n_first = t.m0; kb = ri;
-                } else {
-                    set = ri / steps_set; n_first = (ri - set * steps_set) * kStepK; kb = t.m0 >> 8;
-                }
-                const uint8_t* wbase = args.wgt[set];
-                const long long ebase = static_cast<long long>(t.expert) * args.expert_bytes;
-                long long srcs[kRowsPerLane];
-                int nbulk = 0;
-#pragma unroll
-                for (int i = 0; i < kRowsPerLane; ++i) {
-                    const int row = lane + 32 * i;
-                    const int n = n_first + row;
-                    long long src = -1;  // -1: no row, otherwise aligned byte offset; bit 62 marks manual copy
-                    if (n < N) {
-                        const long long off = ebase + (static_cast<long long>(n) * nkb + kb) * Fmt::kBytes;
-                        src = off & ~15LL;
-                        if (src + Fmt::kCopy > args.wgt_bytes) src |= (1LL << 62);
-                    }
-                    srcs[i] = src;
-                    nbulk += __popc(__ballot_sync(0xFFFFFFFFu, src >= 0 && (src >> 62) == 0));
-                }
-                const uint32_t bar = bar_raw_full + 8 * r;
-                if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(nbulk) * Fmt::kCopy);
-                __syncwarp();
-                const uint32_t stage_s = raw_s + r * Cfg::kRawStageBytes;
-                uint8_t* stage_g = raw_g + r * Cfg::kRawStageBytes;
-#pragma unroll
-                for (int i = 0; i < kRowsPerLane; ++i) {
-                    const int row = lane + 32 * i;
-                    const long long src = srcs[i];
-                    if (src < 0) continue;
-                    if ((src >> 62) == 0) {
-                        bulk_load(stage_s + row * Fmt::kSlot, wbase + src, Fmt::kCopy, bar);
+                if (lane == 0) {
+                    int set, n_first, kb;
+                    if (MODE == kFwd) {
+                        set = t.set; n_first = t.m0; kb = ri;
                     } else {
-                        // last block(s) of the tensor: the 16-byte window would run past the end
-                        const long long s0 = src & ~(1LL << 62);
-                        const int nbytes = static_cast<int>(args.wgt_bytes - s0);  // even
-                        const uint16_t* g16 = reinterpret_cast<const uint16_t*>(wbase + s0);
-                        uint16_t* d16 = reinterpret_cast<uint16_t*>(stage_g + row * Fmt::kSlot);
-                        for (int b = 0; b < nbytes / 2; ++b) d16[b] = g16[b];
+                        set = ri / steps_set; n_first = (ri - set * steps_set) * kStepK; kb = t.m0 >> 8;
+                    }
+                    const long long g0 = static_cast<long long>(t.expert) * N + n_first;  // first global weight row
+                    const uint32_t bar = bar_raw_full + 8 * r;
+                    mbar_arrive_expect_tx(bar, static_cast<uint32_t>(kRows) * Fmt::kCopy);
+                    const uint32_t stage_s = raw_s + r * Cfg::kRawStageBytes;
+                    for (int c = 0; c < P; ++c) {
+                        // first row of class c at or after g0, as a row index inside map c
+                        const long long first = g0 + ((c - g0) & (P - 1));
+                        const int y = static_cast<int>((first - c) >> lgP);
+                        const int mis_c = (c * args.wgt_row_bytes) & 15;
+                        const int x = (mis_c + kb * Fmt::kBytes) & ~15;
+                        tma_load_2d(stage_s + c * (kRows >> lgP) * Fmt::kCopy, &args.wgt_maps[set].cls[c], bar, x, y);
                     }
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar);
             }
         }
     } else if (warp >= 4 && warp < 4 + kDecodeWarps) {
@@ -374,7 +369,6 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
             TileInfo t;
             if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
-            const long long ebase = static_cast<long long>(t.expert) * args.expert_bytes;
             for (int step = 0; step < nsteps; ++step, ++ita) {
                 int row, g, n, kb;
                 uint32_t dst_off;  // byte offset of this thread's first chunk row inside the tile
@@ -407,12 +401,13 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 if (!all_wait(bar_wgt_empty + 8 * sa, pa ^ 1u, abort_word, kAbortWgtEmpty)) { ok = false; break; }
                 uint4 o[4];
                 if (n < N) {
-                    int mis = 0;
-                    if (!Fmt::kAligned) {
-                        const long long off = ebase + (static_cast<long long>(n) * nkb + kb) * Fmt::kBytes;
-                        mis = static_cast<int>(off & 15);
-                    }
-                    const uint8_t* blk = raw_g + r * Cfg::kRawStageBytes + row * Fmt::kSlot + mis;
+                    // where the raw producer put this row: class (alignment of the global row), then row / P
+                    const int P = args.wgt_classes, lgP = args.wgt_classes_log2;
+                    const int c0 = static_cast<int>((static_cast<long long>(t.expert) * N + (n - row)) & (P - 1));
+                    const int cls = (c0 + row) & (P - 1);
+                    const int slot = cls * (Cfg::kRawRows >> lgP) + (row >> lgP);
+                    const int mis = Fmt::kAligned ? 0 : (((cls * args.wgt_row_bytes) & 15) + kb * Fmt::kBytes) & 15;
+                    const uint8_t* blk = raw_g + r * Cfg::kRawStageBytes + slot * Fmt::kCopy + mis;
                     decode32<QT>(blk, g, grid, o);
                 } else {
                     o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);

@@ -104,6 +104,50 @@ static int make_act_maps(ActMaps& maps, const void* base, int64_t rows, int64_t 
     return TGO_OK;
 }
 
+// Packed weight tensor [total_rows][row_bytes] as up to 8 byte-typed 2-D maps, one per alignment
+// class of its rows (see WgtMaps).  Box = one block window (copy_bytes) x box_rows / P rows.
+static int make_wgt_maps(WgtMaps& maps, const void* base, int64_t total_rows, int64_t row_bytes, int copy_bytes,
+                         int box_rows, int& classes, int& classes_log2) {
+    auto encode = encode_fn();
+    if (encode == nullptr) return fail(TGO_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    int g = 16;
+    while (row_bytes % g != 0) g >>= 1;  // gcd(row_bytes, 16); row_bytes is even
+    const int P = 16 / g;
+    classes = P;
+    classes_log2 = P == 1 ? 0 : P == 2 ? 1 : P == 4 ? 2 : 3;
+    const cuuint32_t estride[2] = {1, 1};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(copy_bytes), static_cast<cuuint32_t>(box_rows / P)};
+    for (int c = 0; c < P; ++c) {
+        const uint8_t* b = static_cast<const uint8_t*>(base);
+        cuuint64_t gdim[2], gstride[1] = {static_cast<cuuint64_t>(row_bytes) * P};
+        if (c < total_rows) {
+            const int64_t off = c * row_bytes;
+            b += off & ~15LL;
+            gdim[0] = static_cast<cuuint64_t>((off & 15) + row_bytes);  // last byte of the row, nothing beyond
+            gdim[1] = static_cast<cuuint64_t>((total_rows - c + P - 1) / P);
+        } else {  // fewer rows than classes: an in-bounds dummy, its rows are never decoded
+            gdim[0] = 16;
+            gdim[1] = 1;
+        }
+        const CUresult r = encode(&maps.cls[c], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(b), gdim, gstride,
+                                  box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(TGO_E_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", static_cast<int>(r));
+    }
+    return TGO_OK;
+}
+
+static int copy_bytes_of(int qt) {
+    switch (qt) {
+        case QT_Q3_K: return BlockFmt<QT_Q3_K>::kCopy;
+        case QT_Q4_K: return BlockFmt<QT_Q4_K>::kCopy;
+        case QT_Q5_K: return BlockFmt<QT_Q5_K>::kCopy;
+        case QT_Q6_K: return BlockFmt<QT_Q6_K>::kCopy;
+        default: return BlockFmt<QT_IQ2_S>::kCopy;
+    }
+}
+
 // ------------------------------------------------------------------ tile-list builder
 // Workspace layout: int32 count at byte 0, int4 tasks from byte 16.
 // One CTA: per group, the number of token tiles ceil(rows / 256); exclusive prefix sum; each
@@ -283,6 +327,13 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
         a.out[s] = static_cast<__nv_bfloat16*>(p.out[(p.mode == kFwd && s < p.nsets) ? s : 0]);
     }
     const int64_t bb = tgo_block_bytes(p.qt);
+    if (p.E * p.N > INT32_MAX) return fail(TGO_E_ARG, "experts * out_features exceeds the kernel limit of 2^31-1");
+    for (int s = 0; s < p.nsets; ++s) {
+        rc = make_wgt_maps(a.wgt_maps[s], p.wgt[s], p.E * p.N, (p.K / 256) * bb, copy_bytes_of(p.qt),
+                           p.mode == kFwd ? 128 : 64, a.wgt_classes, a.wgt_classes_log2);
+        if (rc != TGO_OK) return rc;
+    }
+    a.wgt_row_bytes = static_cast<int>((p.K / 256) * bb);
     a.expert_bytes = p.N * (p.K / 256) * bb;
     a.wgt_bytes = a.expert_bytes * p.E;
     a.status = status_ptr();
