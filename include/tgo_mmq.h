@@ -41,6 +41,9 @@ extern "C" {
 #define TGO_Q6_K 14
 #define TGO_IQ2_S 22
 
+/* Most tiles (rows / 256 + groups) tgo_grouped_fwd_noalloc accepts. */
+#define TGO_NOALLOC_MAX_TILES 4096
+
 /* Library version (major*10000 + minor*100 + patch). */
 int tgo_version(void);
 
@@ -103,6 +106,30 @@ int tgo_grouped_dx(const void* dy0, const void* dy1, const void* w0, const void*
                    int64_t num_groups, int64_t num_experts, int64_t rows, int64_t out_features,
                    int64_t in_features, int quant_type, void* workspace, int64_t workspace_bytes,
                    void* stream);
+
+/* Grouped forward for callers that cannot hand over a workspace and must not trigger a device
+ * allocation: the same operation and results as tgo_grouped_fwd, with the tile list kept in a
+ * fixed array inside the library instead of caller memory.  No counterpart in the reference.
+ *
+ * Who needs it: a host runtime that reserved all device memory for its own plan at start-up, an
+ * inference loop that forbids cudaMalloc/cudaFree while serving because they stall every stream of
+ * the device, or a foreign-function binding that only receives input and output buffers and has
+ * no allocator to ask.  This call performs no cudaMalloc, no cudaFree and calls no allocating
+ * library routine; the caller still passes every input and output.
+ *
+ * Limit: rows / 256 + num_groups must not exceed TGO_NOALLOC_MAX_TILES (4096, i.e.
+ * 64 KiB + 16 B of device memory that every GPU loading the library holds until the process
+ * exits); larger problems are rejected with TGO_E_WORKSPACE and must use tgo_grouped_fwd.
+ * The first call on a device looks up the array's device address (the device must be current);
+ * make that first call outside any stream capture.  All calls on a device share the one array,
+ * which keeps whatever the previous call left in it: each call rewrites the count and every
+ * entry it later reads, so nothing has to be cleared, but two calls whose kernels overlap on the
+ * GPU (different streams without an ordering between them) race on it. */
+int tgo_grouped_fwd_noalloc(const void* x, const void* w0, const void* w1, void* y0, void* y1,
+                            const int64_t* expert_indices, const int32_t* expert_offsets,
+                            int64_t num_groups, int64_t num_experts, int64_t rows,
+                            int64_t out_features, int64_t in_features, int quant_type,
+                            void* stream);
 
 #ifdef __cplusplus
 }

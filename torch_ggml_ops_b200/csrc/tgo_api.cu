@@ -365,6 +365,33 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
     return dispatch_gemm(p.qt, p.mode, a, static_cast<int>(grid), stream);
 }
 
+// ------------------------------------------------------------------ built-in tile-list scratch
+// Scratch for tgo_grouped_fwd_noalloc: the tile list lives in this fixed array instead of a
+// caller-provided workspace.  Every GPU that loads the library holds these bytes until exit.
+constexpr int64_t kStaticMaxTiles = TGO_NOALLOC_MAX_TILES;  // most (rows / 256 + groups) it can describe
+constexpr int64_t kStaticScratchBytes = 16 + 16 * kStaticMaxTiles;
+static __device__ __align__(256) unsigned char g_static_tile_scratch[kStaticScratchBytes];
+
+// Device address of the array on the current device.  In host code the array's name is only a
+// handle for the runtime, never an address a kernel may be given, so the address is looked up
+// once per device (with that device current) and remembered.
+static int static_scratch_ptr(void** out) {
+    static void* cached[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(TGO_E_ARG, "device index %d is outside the supported range 0..63", dev);
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_tile_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(built-in tile scratch)");
+        if (p == nullptr) return fail(TGO_E_CUDA, "cudaGetSymbolAddress returned a null address for the built-in tile scratch");
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return TGO_OK;
+}
+
 }  // namespace tgo
 
 // ====================================================================== C ABI
@@ -489,6 +516,22 @@ int tgo_grouped_dx(const void* dy0, const void* dy1, const void* w0, const void*
     p.experts = expert_indices; p.offsets = expert_offsets; p.groups = num_groups;
     p.ws = workspace; p.ws_bytes = workspace_bytes;
     return run_problem(p, static_cast<cudaStream_t>(stream));
+}
+
+int tgo_grouped_fwd_noalloc(const void* x, const void* w0, const void* w1, void* y0, void* y1,
+                            const int64_t* expert_indices, const int32_t* expert_offsets, int64_t num_groups,
+                            int64_t num_experts, int64_t rows, int64_t out_features, int64_t in_features,
+                            int quant_type, void* stream) {
+    if (rows > 0 && num_groups > 0 && task_capacity(rows, num_groups) > kStaticMaxTiles)
+        return fail(TGO_E_WORKSPACE,
+                    "tgo_grouped_fwd_noalloc: rows/256 + groups = %lld exceeds the built-in limit of %lld tiles; "
+                    "use tgo_grouped_fwd with a caller-provided workspace",
+                    (long long)task_capacity(rows, num_groups), (long long)kStaticMaxTiles);
+    void* scratch = nullptr;
+    const int rc = static_scratch_ptr(&scratch);
+    if (rc != TGO_OK) return rc;
+    return tgo_grouped_fwd(x, w0, w1, y0, y1, expert_indices, expert_offsets, num_groups, num_experts, rows,
+                           out_features, in_features, quant_type, scratch, kStaticScratchBytes, stream);
 }
 
 }  // extern "C"

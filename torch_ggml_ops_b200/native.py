@@ -10,6 +10,7 @@ from __future__ import annotations
 import ctypes
 from pathlib import Path
 
+NOALLOC_MAX_TILES = 4096  # TGO_NOALLOC_MAX_TILES in include/tgo_mmq.h
 _LIB_PATH = Path(__file__).resolve().parent / "lib" / "libtgo_mmq.so"
 
 _vp, _i64, _i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
@@ -27,6 +28,7 @@ SIGNATURES = {
     "tgo_build_tiles": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tgo_grouped_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
     "tgo_grouped_dx": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
+    "tgo_grouped_fwd_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
 }
 
 _lib = None
@@ -122,3 +124,13 @@ def grouped_dx(dy0, dy1, w0, w1, dx, expert_indices, expert_offsets, num_experts
                                _ptr(expert_offsets), expert_indices.numel(), num_experts, rows, out_features,
                                in_features, quant_type, _ptr(workspace), workspace.numel(), _stream(stream)),
           "tgo_grouped_dx")
+
+
+def grouped_fwd_noalloc(x, w0, w1, y0, y1, expert_indices, expert_offsets, num_experts, rows, out_features,
+                        in_features, quant_type, stream=None) -> None:
+    """Grouped forward that keeps its tile list in the library's built-in scratch (no workspace
+    argument, no device allocation); see ``tgo_grouped_fwd_noalloc`` in ``include/tgo_mmq.h``."""
+    check(lib().tgo_grouped_fwd_noalloc(_ptr(x), _ptr(w0), _ptr(w1), _ptr(y0), _ptr(y1), _ptr(expert_indices),
+                                        _ptr(expert_offsets), expert_indices.numel(), num_experts, rows,
+                                        out_features, in_features, quant_type, _stream(stream)),
+          "tgo_grouped_fwd_noalloc")
