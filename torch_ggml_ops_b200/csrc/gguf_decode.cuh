@@ -80,22 +80,43 @@ __device__ __forceinline__ void kquant_scale_min(uint32_t s0, uint32_t s1, uint3
     }
 }
 
+// Byte b of v as the float 2^23 + byte (exact); the caller subtracts 2^23 (plus any offset).
+__device__ __forceinline__ float byte_to_biased_float(uint32_t v, int b) {
+    return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650u + b));
+}
+// Two weights at once with the packed fp32x2 instructions of sm_100 (each half is an ordinary
+// IEEE fp32 operation, so results are bit-identical to the scalar formulas):
+//   affine: (q - 0) * ds - mn as one fused multiply-add per half;  scaled: (q - off) * ds.
+__device__ __forceinline__ uint32_t affine2(uint32_t v, int b0, int b1, float2 ds, float2 neg_mn) {
+    const float2 f = make_float2(byte_to_biased_float(v, b0), byte_to_biased_float(v, b1));
+    const float2 q = __fadd2_rn(f, make_float2(-8388608.0f, -8388608.0f));
+    const float2 w = __ffma2_rn(ds, q, neg_mn);
+    return pack_bf16(w.x, w.y);
+}
+__device__ __forceinline__ uint32_t scaled2(uint32_t v, int b0, int b1, float2 ds, float2 neg_bias) {
+    const float2 f = make_float2(byte_to_biased_float(v, b0), byte_to_biased_float(v, b1));
+    const float2 q = __fadd2_rn(f, neg_bias);
+    const float2 w = __fmul2_rn(ds, q);
+    return pack_bf16(w.x, w.y);
+}
 // Eight weights from two words of byte-sized quants: w = ds * q - mn.
 __device__ __forceinline__ uint4 affine8(uint32_t v0, uint32_t v1, float ds, float mn) {
+    const float2 ds2 = make_float2(ds, ds), nm2 = make_float2(-mn, -mn);
     uint4 o;
-    o.x = pack_bf16(ds * byte_to_float(v0, 0) - mn, ds * byte_to_float(v0, 1) - mn);
-    o.y = pack_bf16(ds * byte_to_float(v0, 2) - mn, ds * byte_to_float(v0, 3) - mn);
-    o.z = pack_bf16(ds * byte_to_float(v1, 0) - mn, ds * byte_to_float(v1, 1) - mn);
-    o.w = pack_bf16(ds * byte_to_float(v1, 2) - mn, ds * byte_to_float(v1, 3) - mn);
+    o.x = affine2(v0, 0, 1, ds2, nm2);
+    o.y = affine2(v0, 2, 3, ds2, nm2);
+    o.z = affine2(v1, 0, 1, ds2, nm2);
+    o.w = affine2(v1, 2, 3, ds2, nm2);
     return o;
 }
 // Eight weights from two words of byte-sized quants with an integer offset: w = ds * (q - off).
 __device__ __forceinline__ uint4 scaled8(uint32_t v0, uint32_t v1, float ds, float off) {
+    const float2 ds2 = make_float2(ds, ds), nb2 = make_float2(-8388608.0f - off, -8388608.0f - off);
     uint4 o;
-    o.x = pack_bf16(ds * (byte_to_float(v0, 0) - off), ds * (byte_to_float(v0, 1) - off));
-    o.y = pack_bf16(ds * (byte_to_float(v0, 2) - off), ds * (byte_to_float(v0, 3) - off));
-    o.z = pack_bf16(ds * (byte_to_float(v1, 0) - off), ds * (byte_to_float(v1, 1) - off));
-    o.w = pack_bf16(ds * (byte_to_float(v1, 2) - off), ds * (byte_to_float(v1, 3) - off));
+    o.x = scaled2(v0, 0, 1, ds2, nb2);
+    o.y = scaled2(v0, 2, 3, ds2, nb2);
+    o.z = scaled2(v1, 0, 1, ds2, nb2);
+    o.w = scaled2(v1, 2, 3, ds2, nb2);
     return o;
 }
 
@@ -224,17 +245,20 @@ __device__ __forceinline__ void decode32<QT_IQ2_S>(const uint8_t* blk, int g, co
         const uint32_t m0 = static_cast<uint32_t>(mags), m1 = static_cast<uint32_t>(mags >> 32);
         const uint32_t sg = (sgnw[0] >> (8 * c)) & 0xFFu;
         const float db = c < 2 ? db0 : db1;
-        float v[8];
+        const uint32_t dbb = __float_as_uint(db);
+        uint32_t o[4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float mag = byte_to_float(e < 4 ? m0 : m1, e & 3);
-            const float w = db * mag;
-            v[e] = __uint_as_float(__float_as_uint(w) ^ (((sg >> e) & 1u) << 31));
+        for (int e = 0; e < 8; e += 2) {
+            const uint32_t mw = e < 4 ? m0 : m1;
+            const float2 f = make_float2(byte_to_biased_float(mw, e & 3), byte_to_biased_float(mw, (e & 3) + 1));
+            const float2 mag = __fadd2_rn(f, make_float2(-8388608.0f, -8388608.0f));
+            // +-db per weight: the sign bit of the sign byte moved onto the float's sign
+            const float2 sdb = make_float2(__uint_as_float(dbb ^ ((sg << (31 - e)) & 0x80000000u)),
+                                           __uint_as_float(dbb ^ ((sg << (30 - e)) & 0x80000000u)));
+            const float2 w = __fmul2_rn(sdb, mag);
+            o[e >> 1] = pack_bf16(w.x, w.y);
         }
-        out[c].x = pack_bf16(v[0], v[1]);
-        out[c].y = pack_bf16(v[2], v[3]);
-        out[c].z = pack_bf16(v[4], v[5]);
-        out[c].w = pack_bf16(v[6], v[7]);
+        out[c] = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
 

@@ -16,14 +16,16 @@
 // The reduction order of every output element is fixed (ascending reduction index, 16 per UMMA),
 // independent of tiling, which makes grouped == dense and pair == two singles bit-exact.
 //
-// Warp roles (512 threads): 0 activation producer (TMA), 1 UMMA issuer + TMEM owner, 2 raw
-// weight producer (bulk copies), 3 idle, 4-11 decode, 12-15 epilogue (TMEM -> bf16 -> global).
+// Warp roles (768 threads): 0 activation producer (TMA), 1 UMMA issuer + TMEM owner, 2 raw
+// weight producer (TMA), 3 idle, 4-19 decode (two groups of 8 warps on alternate steps), 20-23
+// epilogue (TMEM -> bf16 -> global).
 // All waits are bounded (ptx.cuh); a wait that gives up unwinds every role to the common exit,
 // which frees TMEM and records a status code.
 #pragma once
 
 #include "gguf_decode.cuh"
 #include "ptx.cuh"
+#include <cstdio>
 
 namespace tgo {
 
@@ -34,12 +36,22 @@ constexpr int kTileTok = 256;        // most tokens per tile (TMEM columns of on
 constexpr int kStepK = 64;           // reduction elements per pipeline step (one swizzle row)
 constexpr int kActTileBytes = kTileTok * 128;
 constexpr int kWgtTileBytes = kTileM * 128;
-constexpr int kActStages = 4;
-constexpr int kDecodeWarps = 8;
-constexpr int kGemmThreads = 512;
+#ifndef TGO_ACT_STAGES
+#define TGO_ACT_STAGES 4
+#endif
+#ifndef TGO_WGT_STAGES_MAX
+#define TGO_WGT_STAGES_MAX 3
+#endif
+constexpr int kActStages = TGO_ACT_STAGES;
+constexpr int kDecodeWarps = 8;        // warps of one decode group (256 threads x 32 weights = one step)
+constexpr int kDecodeGroups = 2;       // groups take alternate steps, so two steps decode at once
+constexpr int kFirstDecodeWarp = 4;
+constexpr int kFirstEpilogueWarp = kFirstDecodeWarp + kDecodeWarps * kDecodeGroups;  // multiple of 4
+constexpr int kGemmThreads = (kFirstEpilogueWarp + 4) * 32;
 constexpr int kTmemCols = 512;       // two accumulators of 256 columns
 constexpr int kNumBoxes = 5;         // activation TMA boxes of 256, 128, 64, 32, 16 rows
 constexpr int kSmemLimit = 232448;   // 227 KB opt-in limit per CTA
+constexpr int kEpiStageBytes = 4 * 32 * 64;  // per epilogue warp: 32 tokens x 32 outputs, bf16
 
 struct ActMaps {
     CUtensorMap box[kNumBoxes];
@@ -88,10 +100,10 @@ struct GemmCfg {
     static constexpr int kRawStageBytes = kRawRows * Fmt::kCopy;
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kGridBytes = QT == QT_IQ2_S ? 8192 : 0;
-    static constexpr int kFixed = 1024 /*alignment slack*/ + 512 /*barriers etc.*/ + 128 /*read slack*/ +
+    static constexpr int kFixed = 1024 /*alignment slack*/ + 512 /*barriers etc.*/ + 128 /*read slack*/ + kEpiStageBytes +
                                   kActStages * kActTileBytes + kRawBytes + kGridBytes;
     static constexpr int kWgtStagesFit = (kSmemLimit - kFixed) / kWgtTileBytes;
-    static constexpr int kWgtStages = kWgtStagesFit >= 3 ? 3 : kWgtStagesFit;
+    static constexpr int kWgtStages = kWgtStagesFit >= TGO_WGT_STAGES_MAX ? TGO_WGT_STAGES_MAX : kWgtStagesFit;
     static_assert(kWgtStages >= 2, "shared memory budget");
     static constexpr int kSmemBytes = kFixed + kWgtStages * kWgtTileBytes;
 };
@@ -137,9 +149,26 @@ __device__ __forceinline__ bool lane0_wait(uint32_t bar, uint32_t parity, volati
 // Every lane waits (each needs the acquire), the warp agrees on the outcome.
 __device__ __forceinline__ bool all_wait(uint32_t bar, uint32_t parity, volatile int* abort_word,
                                          int code) {
+#ifdef TGO_EXP_LOWPOLL
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_word, code) ? 1 : 0;
+    __syncwarp();
+    return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+#else
     const bool ok = mbar_wait(bar, parity, abort_word, code);
     return __all_sync(0xFFFFFFFFu, ok) != 0;
+#endif
 }
+
+// Optional per-role cycle accounting (compile with -DTGO_ROLE_TIMERS): CTA 0 prints, for one lane
+// of each role, the cycles spent in each wait and in its own work.  Off in the product build.
+#ifdef TGO_ROLE_TIMERS
+#define TGO_T0() const long long tgo_t0_ = clock64()
+#define TGO_ACC(var) var += clock64() - tgo_t0_
+#define TGO_TIMED(var, expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); var += clock64() - t_; return r_; }()
+#else
+#define TGO_TIMED(var, expr) (expr)
+#endif
 
 template <int QT, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -160,8 +189,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     uint8_t* wgt_g = act_g + NB * kActTileBytes;
     uint8_t* raw_g = wgt_g + NA * kWgtTileBytes;
     uint8_t* grid_g = raw_g + Cfg::kRawBytes + 128;
-    uint8_t* misc_g = grid_g + Cfg::kGridBytes;
-    const uint32_t misc_s = raw_s + Cfg::kRawBytes + 128 + Cfg::kGridBytes;
+    uint8_t* epi_g = grid_g + Cfg::kGridBytes;
+    uint8_t* misc_g = epi_g + kEpiStageBytes;
+    const uint32_t misc_s = raw_s + Cfg::kRawBytes + 128 + Cfg::kGridBytes + kEpiStageBytes;
     // barriers (8 bytes each)
     const uint32_t bar_act_full = misc_s;                    // NB
     const uint32_t bar_act_empty = bar_act_full + 8 * NB;    // NB
@@ -179,6 +209,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    long long tw0 = 0, tw1 = 0, tw2 = 0, twork = 0, twork2 = 0;  // role timers (unused unless TGO_ROLE_TIMERS)
+    (void)tw0; (void)tw1; (void)tw2; (void)twork; (void)twork2;
+    const long long t_kernel0 = clock64();
 
     const int N = args.out_features, K = args.in_features;
     const int nkb = K >> 8;
@@ -193,7 +226,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     if (threadIdx.x == 0) {
         for (int i = 0; i < NB; ++i) { mbar_init(bar_act_full + 8 * i, 1); mbar_init(bar_act_empty + 8 * i, 1); }
         for (int i = 0; i < NA; ++i) { mbar_init(bar_wgt_full + 8 * i, kDecodeWarps); mbar_init(bar_wgt_empty + 8 * i, 1); }
-        for (int i = 0; i < NR; ++i) { mbar_init(bar_raw_full + 8 * i, 1); mbar_init(bar_raw_empty + 8 * i, kDecodeWarps); }
+        for (int i = 0; i < NR; ++i) { mbar_init(bar_raw_full + 8 * i, 1); mbar_init(bar_raw_empty + 8 * i, MODE == kFwd ? kDecodeWarps * kDecodeGroups : kDecodeWarps); }
         for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, 4); }
         *abort_word = 0;
         mbar_fence_init();
@@ -225,11 +258,14 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
                 for (int step = 0; step < nsteps; ++step, ++it) {
                     const uint32_t s = it % NB, ph = (it / NB) & 1u;
-                    if (!lane0_wait(bar_act_empty + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty, lane)) { ok = false; break; }
+                    if (!TGO_TIMED(tw0, lane0_wait(bar_act_empty + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty, lane))) { ok = false; break; }
                     if (lane == 0) {
                         const int set = MODE == kFwd ? 0 : step / steps_set;
                         const int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
                         const uint32_t bar = bar_act_full + 8 * s;
+#ifdef TGO_EXP_NO_ACT
+                        mbar_arrive(bar);
+#else
                         mbar_arrive_expect_tx(bar, static_cast<uint32_t>(t.ntok_pad) * 128u);
                         uint32_t dst = act_s + s * kActTileBytes;
                         int row = t.row0, rem = t.ntok_pad;
@@ -243,6 +279,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                                 rem -= h;
                             }
                         }
+#endif
                     }
                     __syncwarp();
                 }
@@ -291,7 +328,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
             const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
             ++tl;
-            if (!lane0_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kAbortAccEmpty, lane)) break;
+            if (!TGO_TIMED(tw2, lane0_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kAbortAccEmpty, lane))) break;
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + acc * kTileTok;
             const uint32_t idesc =
@@ -299,9 +336,12 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             for (int step = 0; step < nsteps; ++step, ++ita, ++itb) {
                 const uint32_t sa = ita % NA, pa = (ita / NA) & 1u;
                 const uint32_t sb = itb % NB, pb = (itb / NB) & 1u;
-                if (!lane0_wait(bar_wgt_full + 8 * sa, pa, abort_word, kAbortWgtFull, lane)) { ok = false; break; }
-                if (!lane0_wait(bar_act_full + 8 * sb, pb, abort_word, kAbortActFull, lane)) { ok = false; break; }
+                if (!TGO_TIMED(tw0, lane0_wait(bar_wgt_full + 8 * sa, pa, abort_word, kAbortWgtFull, lane))) { ok = false; break; }
+                if (!TGO_TIMED(tw1, lane0_wait(bar_act_full + 8 * sb, pb, abort_word, kAbortActFull, lane))) { ok = false; break; }
                 if (lane == 0) {
+#ifdef TGO_ROLE_TIMERS
+                    const long long t_i0 = clock64();
+#endif
                     tc_fence_after_sync();
                     const uint32_t wa = wgt_s + sa * kWgtTileBytes;
                     const uint32_t ba = act_s + sb * kActTileBytes;
@@ -310,10 +350,19 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                         const uint64_t adesc = MODE == kFwd ? umma_smem_desc(wa + kk * 32, 16, 1024)
                                                             : umma_smem_desc(wa + kk * 2048, 8192, 1024);
                         const uint64_t bdesc = umma_smem_desc(ba + kk * 32, 16, 1024);
+#ifndef TGO_EXP_NO_MMA
                         umma_bf16(d_tmem, adesc, bdesc, idesc, (step | kk) != 0 ? 1u : 0u);
+#endif
                     }
+#ifdef TGO_ROLE_TIMERS
+                    const long long t_i1 = clock64();
+                    twork += t_i1 - t_i0;
+#endif
                     umma_commit(bar_wgt_empty + 8 * sa);
                     umma_commit(bar_act_empty + 8 * sb);
+#ifdef TGO_ROLE_TIMERS
+                    twork2 += clock64() - t_i1;
+#endif
                 }
                 __syncwarp();
             }
@@ -337,7 +386,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             const int nraw = MODE == kFwd ? nkb : nsteps;
             for (int ri = 0; ri < nraw; ++ri, ++itr) {
                 const uint32_t r = itr % NR, ph = (itr / NR) & 1u;
-                if (!lane0_wait(bar_raw_empty + 8 * r, ph ^ 1u, abort_word, kAbortRawEmpty, lane)) { ok = false; break; }
+                if (!TGO_TIMED(tw0, lane0_wait(bar_raw_empty + 8 * r, ph ^ 1u, abort_word, kAbortRawEmpty, lane))) { ok = false; break; }
                 if (lane == 0) {
                     int set, n_first, kb;
                     if (MODE == kFwd) {
@@ -347,9 +396,15 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     }
                     const long long g0 = static_cast<long long>(t.expert) * N + n_first;  // first global weight row
                     const uint32_t bar = bar_raw_full + 8 * r;
+#ifdef TGO_EXP_NO_RAW
+                    mbar_arrive(bar);
+                    const uint32_t stage_s = raw_s + r * Cfg::kRawStageBytes;
+                    for (int c = 0; c < 0; ++c) {
+#else
                     mbar_arrive_expect_tx(bar, static_cast<uint32_t>(kRows) * Fmt::kCopy);
                     const uint32_t stage_s = raw_s + r * Cfg::kRawStageBytes;
                     for (int c = 0; c < P; ++c) {
+#endif
                         // first row of class c at or after g0, as a row index inside map c
                         const long long first = g0 + ((c - g0) & (P - 1));
                         const int y = static_cast<int>((first - c) >> lgP);
@@ -361,9 +416,12 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 __syncwarp();
             }
         }
-    } else if (warp >= 4 && warp < 4 + kDecodeWarps) {
+    } else if (warp >= kFirstDecodeWarp && warp < kFirstEpilogueWarp) {
         // ------------------------------------------------------------ decode warps
-        const int dt = threadIdx.x - 128;  // 0..255
+        // Group g decodes the steps whose running index is g (mod kDecodeGroups).  Forward: one raw
+        // stage (a super-block column) serves four steps, two per group; backward: one per step.
+        const int group = (warp - kFirstDecodeWarp) / kDecodeWarps;
+        const int dt = threadIdx.x - (kFirstDecodeWarp + group * kDecodeWarps) * 32;  // 0..255
         uint32_t ita = 0, itr = 0;
         bool ok = true;
         for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
@@ -392,26 +450,46 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     cbase = 4 * (q & 1);
                 }
                 const uint32_t r = itr % NR, rph = (itr / NR) & 1u;
-                const bool first_use = MODE == kFwd ? (step & 3) == 0 : true;
-                const bool last_use = MODE == kFwd ? (step & 3) == 3 : true;
+                // forward: steps 4b..4b+3 share raw stage b; this group touches steps g and g+2 of them
+                const bool first_use = MODE == kFwd ? (step & 3) == group : true;
+                const bool last_use = MODE == kFwd ? (step & 3) == group + 2 : true;
+                const bool stage_done = MODE == kFwd ? (step & 3) == 3 : true;
+                if (static_cast<int>(ita % kDecodeGroups) != group) {
+                    if (stage_done) ++itr;
+                    continue;
+                }
                 if (first_use) {
-                    if (!all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull)) { ok = false; break; }
+                    if (!TGO_TIMED(tw0, all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull))) { ok = false; break; }
                 }
                 const uint32_t sa = ita % NA, pa = (ita / NA) & 1u;
-                if (!all_wait(bar_wgt_empty + 8 * sa, pa ^ 1u, abort_word, kAbortWgtEmpty)) { ok = false; break; }
+                if (!TGO_TIMED(tw1, all_wait(bar_wgt_empty + 8 * sa, pa ^ 1u, abort_word, kAbortWgtEmpty))) { ok = false; break; }
+#ifdef TGO_ROLE_TIMERS
+                const long long t_dec0 = clock64();
+#endif
                 uint4 o[4];
+#ifdef TGO_EXP_NO_DECODE
+                if (false) {
+#else
                 if (n < N) {
+#endif
                     // where the raw producer put this row: class (alignment of the global row), then row / P
-                    const int P = args.wgt_classes, lgP = args.wgt_classes_log2;
-                    const int c0 = static_cast<int>((static_cast<long long>(t.expert) * N + (n - row)) & (P - 1));
-                    const int cls = (c0 + row) & (P - 1);
-                    const int slot = cls * (Cfg::kRawRows >> lgP) + (row >> lgP);
-                    const int mis = Fmt::kAligned ? 0 : (((cls * args.wgt_row_bytes) & 15) + kb * Fmt::kBytes) & 15;
+                    int slot = row, mis = 0;
+                    if (!Fmt::kAligned) {
+                        const int P = args.wgt_classes, lgP = args.wgt_classes_log2;
+                        const int c0 = static_cast<int>((static_cast<long long>(t.expert) * N + (n - row)) & (P - 1));
+                        const int cls = (c0 + row) & (P - 1);
+                        slot = cls * (Cfg::kRawRows >> lgP) + (row >> lgP);
+                        mis = (((cls * args.wgt_row_bytes) & 15) + kb * Fmt::kBytes) & 15;
+                    }
                     const uint8_t* blk = raw_g + r * Cfg::kRawStageBytes + slot * Fmt::kCopy + mis;
                     decode32<QT>(blk, g, grid, o);
                 } else {
                     o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
                 }
+#ifdef TGO_ROLE_TIMERS
+                const long long t_dec1 = clock64();
+                twork2 += t_dec1 - t_dec0;
+#endif
                 uint8_t* tile_g = wgt_g + sa * kWgtTileBytes + dst_off;
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
@@ -422,10 +500,13 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     mbar_arrive(bar_wgt_full + 8 * sa);
                     if (last_use) mbar_arrive(bar_raw_empty + 8 * r);
                 }
-                if (last_use) ++itr;
+#ifdef TGO_ROLE_TIMERS
+                twork += clock64() - t_dec0;
+#endif
+                if (stage_done) ++itr;
             }
         }
-    } else if (warp >= 12) {
+    } else if (warp >= kFirstEpilogueWarp) {
         // ------------------------------------------------------------ epilogue
         const int quad = warp & 3;
         uint32_t tl = 0;
@@ -435,30 +516,73 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
             const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
             ++tl;
-            if (!all_wait(bar_acc_full + 8 * acc, aph, abort_word, kAbortAccFull)) break;
+            if (!TGO_TIMED(tw0, all_wait(bar_acc_full + 8 * acc, aph, abort_word, kAbortAccFull))) break;
+#ifdef TGO_ROLE_TIMERS
+            const long long t_ep0 = clock64();
+#endif
             tc_fence_after_sync();
-            const int m = t.m0 + quad * 32 + lane;
-            const bool m_ok = m < mdim;
-            __nv_bfloat16* out = args.out[MODE == kFwd ? t.set : 0] + static_cast<long long>(t.row0) * mdim + m;
             const uint32_t taddr = tmem_base + acc * kTileTok + (static_cast<uint32_t>(quad * 32) << 16);
-            for (int c0 = 0; c0 < t.ntok_pad; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(taddr + c0, v);
-                tmem_ld_wait();
-                if (m_ok) {
+            const int mq = t.m0 + quad * 32;  // first output column of this warp
+            __nv_bfloat16* out_base = args.out[MODE == kFwd ? t.set : 0] + static_cast<long long>(t.row0) * mdim;
+            if ((mdim & 7) == 0 && mq + 32 <= mdim) {
+                // Transposing path: the warp's 32 outputs x 32 tokens go through a private staging
+                // tile [token][32 outputs] so that global stores are 16 bytes per lane.
+                uint8_t* stage = epi_g + quad * (32 * 64);
+                for (int c0 = 0; c0 < t.ntok_pad; c0 += 32) {
+                    uint32_t v[32];
+                    if (c0 + 32 <= t.ntok_pad) {
+                        tmem_ld32(taddr + c0, v);
+                    } else {  // last 16 padded columns of the tile
+                        uint32_t h[16];
+                        tmem_ld16(taddr + c0, h);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (c0 + j < t.ntok)
-                            out[static_cast<long long>(c0 + j) * mdim] = __float2bfloat16(__uint_as_float(v[j]));
+                        for (int j = 0; j < 16; ++j) { v[j] = h[j]; v[16 + j] = 0u; }
+                    }
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        *reinterpret_cast<__nv_bfloat16*>(stage + j * 64 + lane * 2) =
+                            __float2bfloat16(__uint_as_float(v[j]));
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = (lane >> 2) + 8 * i, part = lane & 3;
+                        const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 64 + part * 16);
+                        if (c0 + r < t.ntok)
+                            *reinterpret_cast<uint4*>(out_base + static_cast<long long>(c0 + r) * mdim + mq + part * 8) = val;
+                    }
+                    __syncwarp();
+                }
+            } else {
+                const int m = mq + lane;
+                const bool m_ok = m < mdim;
+                __nv_bfloat16* out = out_base + m;
+                for (int c0 = 0; c0 < t.ntok_pad; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + c0, v);
+                    tmem_ld_wait();
+                    if (m_ok) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (c0 + j < t.ntok)
+                                out[static_cast<long long>(c0 + j) * mdim] = __float2bfloat16(__uint_as_float(v[j]));
+                        }
                     }
                 }
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+#ifdef TGO_ROLE_TIMERS
+            twork += clock64() - t_ep0;
+#endif
         }
     }
 
+#ifdef TGO_ROLE_TIMERS
+    if (blockIdx.x == 0 && lane == 0 && (warp <= 2 || warp == kFirstDecodeWarp || warp == kFirstDecodeWarp + kDecodeWarps || warp == kFirstEpilogueWarp))
+        printf("role warp %2d: wait0 %9lld wait1 %9lld wait2 %9lld work %9lld work2 %9lld total %9lld\n", warp, tw0, tw1, tw2, twork, twork2, clock64() - t_kernel0);
+#endif
     // ------------------------------------------------------------ common exit
     if (*abort_word != 0) {
         // Some wait gave up.  Give copies and UMMAs still in flight a bounded time to land before
