@@ -107,6 +107,42 @@ int tgo_grouped_dx(const void* dy0, const void* dy1, const void* w0, const void*
                    int64_t in_features, int quant_type, void* workspace, int64_t workspace_bytes,
                    void* stream);
 
+/* ---- routing helpers (the steps either side of the grouped projections) ------------------------
+ * The reference takes rows that its caller already sorted by expert; these entry points do that
+ * sort, the gather and the top-k combine on the device with no device-to-host read (every expert
+ * gets a group, empty ones included, so the group count is the static expert count). */
+
+/* Workspace bytes for tgo_route_sort. */
+int64_t tgo_route_workspace_bytes(int64_t n_pairs, int64_t num_experts);
+
+/* Stable counting sort of routed (token, slot) pairs by expert id.  expert_ids int32[n_pairs]
+ * (pair index = token * top_k + slot); outputs: sorted_to_pair int32[n_pairs] (pair held by each
+ * sorted row), pair_to_sorted int32[n_pairs] (its inverse; -1 for an out-of-range id),
+ * expert_indices int64[E] = 0..E-1 and expert_offsets int32[E] = cumulative end rows: exactly the
+ * metadata of validate_grouped_mmq (csrc/mmq_hip.cu:325-406).  Device prefix sum; counterpart of
+ * the reference's only device scan, grouped_mmq_build_row_tasks (csrc/mmq_core.cuh:516-571). */
+int tgo_route_sort(const int32_t* expert_ids, int64_t n_pairs, int64_t num_experts,
+                   int32_t* sorted_to_pair, int32_t* pair_to_sorted, int64_t* expert_indices,
+                   int32_t* expert_offsets, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* dst[r][:] = src[index[r] / divisor][:] for bf16 rows of `width` (a multiple of 8); with
+ * index = sorted_to_pair and divisor = top_k this builds the expert-sorted activation rows. */
+int tgo_gather_rows(const void* src, const int32_t* index, int64_t divisor, void* dst,
+                    int64_t n_rows, int64_t width, void* stream);
+
+/* out[t][:] = sum over slots of weights[t][slot] * rows[pair_to_sorted[t*top_k+slot]][:] (fp32
+ * accumulation, one bf16 rounding; weights may be null = 1). */
+int tgo_combine_rows(const void* rows, const int32_t* pair_to_sorted, const float* weights,
+                     void* out, int64_t tokens, int64_t top_k, int64_t width, void* stream);
+
+/* bf16 activations [rows][width] -> q8_1-style blocks of 32 values: int8 quants q[rows][width],
+ * fp32 scales d[rows][width/32] = amax/127 and fp32 sums of the unquantised values
+ * sum[rows][width/32].  Replaces quantize_bf16_mmq_q8_1 (csrc/mmq_core.cuh:151-209), with fp32
+ * instead of fp16 scales.  Not used by the bf16-dequant matmul path; provided for the int8
+ * variant of the forward. */
+int tgo_quantize_q8(const void* x, int64_t rows, int64_t width, void* q, float* d, float* sum,
+                    void* stream);
+
 /* Grouped forward for callers that cannot hand over a workspace and must not trigger a device
  * allocation: the same operation and results as tgo_grouped_fwd, with the tile list kept in a
  * fixed array inside the library instead of caller memory.  No counterpart in the reference.

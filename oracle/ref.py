@@ -213,3 +213,19 @@ def rel_frobenius(test, ref) -> float:
     num = torch.linalg.vector_norm((test - ref)[mask])
     den = torch.linalg.vector_norm(ref[mask])
     return float(num / den) if float(den) > 0 else float(num)
+
+
+def quantize_q8(x):
+    """q8_1-style activation blocks of 32 values (csrc/mmq_core.cuh:151-209): returns
+    (int8 quants, fp32 d = amax/127, fp32 sum of the unquantised values), numpy arrays.
+    ``x``: torch tensor [rows, width] of any float dtype, width a multiple of 32."""
+    xf = x.to(__import__("torch").float32).numpy()
+    rows, width = xf.shape
+    b = xf.reshape(rows, width // 32, 32)
+    amax = np.abs(b).max(axis=2)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        inv = np.where(amax > 0, np.float32(127.0) / amax, np.float32(0)).astype(np.float32)
+        d = np.where(amax > 0, amax / np.float32(127.0), np.float32(0)).astype(np.float32)
+    scaled = b * inv[:, :, None]
+    q = (np.sign(scaled) * np.floor(np.abs(scaled) + np.float32(0.5))).astype(np.int8)  # roundf: half away from zero
+    return q.reshape(rows, width), d, b.sum(axis=2, dtype=np.float64).astype(np.float32)

@@ -34,29 +34,52 @@ __host__ __device__ constexpr int block_bytes_of(int qt) {
          : qt == QT_IQ2_S ? 82 : -1;
 }
 
+// Shared-memory accesses by 32-bit shared-window address (one integer add per access instead of
+// 64-bit generic pointer arithmetic).
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint32_t v;
+    asm volatile("{ .reg .u16 h; ld.shared.u16 h, [%1]; cvt.u32.u16 %0, h; }" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t a, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 // N consecutive 32-bit words starting at a 2-byte-aligned shared-memory address.
 template <int N>
-__device__ __forceinline__ void ld_words(const uint8_t* p, uint32_t (&w)[N]) {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    const uint32_t* base = reinterpret_cast<const uint32_t*>(a & ~static_cast<uintptr_t>(3));
-    const uint32_t sh = (static_cast<uint32_t>(a) & 2u) * 8u;
-    uint32_t prev = base[0];
+__device__ __forceinline__ void ld_words(uint32_t a, uint32_t (&w)[N]) {
+    const uint32_t base = a & ~3u;
+    const uint32_t sh = (a & 2u) * 8u;
+    uint32_t prev = lds32(base);
 #pragma unroll
     for (int i = 0; i < N; ++i) {
-        const uint32_t next = base[i + 1];
+        const uint32_t next = lds32(base + 4 * (i + 1));
         w[i] = __funnelshift_r(prev, next, sh);
         prev = next;
     }
 }
-__device__ __forceinline__ uint32_t ld_u16(const uint8_t* p) {
-    return *reinterpret_cast<const uint16_t*>(p);
-}
 __device__ __forceinline__ float half_bits_to_float(uint32_t h) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
-}
-// Byte b of v as an exact float: 2^23 + byte, minus 2^23.
-__device__ __forceinline__ float byte_to_float(uint32_t v, int b) {
-    return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650u + b)) - 8388608.0f;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
@@ -120,22 +143,21 @@ __device__ __forceinline__ uint4 scaled8(uint32_t v0, uint32_t v1, float ds, flo
     return o;
 }
 
-// decode32<QT>: weights 32g .. 32g+31 of the block at `blk` (shared memory), as four 16-byte
-// chunks of 8 bf16 each.  `grid` is the IQ2_S codebook in shared memory (unused otherwise).
+// decode32<QT>: weights 32g .. 32g+31 of the block at shared-memory address `blk`, as four
+// 16-byte chunks of 8 bf16 each.  `grid` is the shared-memory address of the IQ2_S codebook
+// (unused otherwise).
 template <int QT>
-__device__ __forceinline__ void decode32(const uint8_t* blk, int g, const uint64_t* grid,
-                                         uint4 (&out)[4]);
+__device__ __forceinline__ void decode32(uint32_t blk, int g, uint32_t grid, uint4 (&out)[4]);
 
 template <>
-__device__ __forceinline__ void decode32<QT_Q4_K>(const uint8_t* blk, int g, const uint64_t*,
-                                                  uint4 (&out)[4]) {
-    const uint4 head = *reinterpret_cast<const uint4*>(blk);  // d, dmin, scales[12]
+__device__ __forceinline__ void decode32<QT_Q4_K>(uint32_t blk, int g, uint32_t, uint4 (&out)[4]) {
+    const uint4 head = lds128(blk);  // d, dmin, scales[12]
     int sc, mn;
     kquant_scale_min(head.y, head.z, head.w, g, sc, mn);
     const float ds = half_bits_to_float(head.x & 0xFFFFu) * static_cast<float>(sc);
     const float dm = half_bits_to_float(head.x >> 16) * static_cast<float>(mn);
-    const uint4* qs = reinterpret_cast<const uint4*>(blk + 16 + (g >> 1) * 32);
-    const uint4 a = qs[0], b = qs[1];
+    const uint32_t qs = blk + 16 + (g >> 1) * 32;
+    const uint4 a = lds128(qs), b = lds128(qs + 16);
     const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     const int sh = 4 * (g & 1);
 #pragma unroll
@@ -147,18 +169,16 @@ __device__ __forceinline__ void decode32<QT_Q4_K>(const uint8_t* blk, int g, con
 }
 
 template <>
-__device__ __forceinline__ void decode32<QT_Q5_K>(const uint8_t* blk, int g, const uint64_t*,
-                                                  uint4 (&out)[4]) {
-    const uint4 head = *reinterpret_cast<const uint4*>(blk);
+__device__ __forceinline__ void decode32<QT_Q5_K>(uint32_t blk, int g, uint32_t, uint4 (&out)[4]) {
+    const uint4 head = lds128(blk);
     int sc, mn;
     kquant_scale_min(head.y, head.z, head.w, g, sc, mn);
     const float ds = half_bits_to_float(head.x & 0xFFFFu) * static_cast<float>(sc);
     const float dm = half_bits_to_float(head.x >> 16) * static_cast<float>(mn);
-    const uint4* qh = reinterpret_cast<const uint4*>(blk + 16);
-    const uint4 ha = qh[0], hb = qh[1];
+    const uint4 ha = lds128(blk + 16), hb = lds128(blk + 32);
     const uint32_t h[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
-    const uint4* qs = reinterpret_cast<const uint4*>(blk + 48 + (g >> 1) * 32);
-    const uint4 a = qs[0], b = qs[1];
+    const uint32_t qs = blk + 48 + (g >> 1) * 32;
+    const uint4 a = lds128(qs), b = lds128(qs + 16);
     const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     const int sh = 4 * (g & 1);
 #pragma unroll
@@ -171,16 +191,15 @@ __device__ __forceinline__ void decode32<QT_Q5_K>(const uint8_t* blk, int g, con
 }
 
 template <>
-__device__ __forceinline__ void decode32<QT_Q6_K>(const uint8_t* blk, int g, const uint64_t*,
-                                                  uint4 (&out)[4]) {
+__device__ __forceinline__ void decode32<QT_Q6_K>(uint32_t blk, int g, uint32_t, uint4 (&out)[4]) {
     // weights i = 32g + j: chunk c = g>>2 of 128; ql byte c*64 + (g&1)*32 + j, nibble (g&3)>>1;
     // qh byte c*32 + j, bit pair g&3; one int8 scale per 16 weights.
     const int c128 = g >> 2;
     uint32_t ql[8], qh[8];
     ld_words<8>(blk + c128 * 64 + (g & 1) * 32, ql);
     ld_words<8>(blk + 128 + c128 * 32, qh);
-    const uint32_t sc2 = ld_u16(blk + 192 + 2 * g);
-    const float d = half_bits_to_float(ld_u16(blk + 208));
+    const uint32_t sc2 = lds16(blk + 192 + 2 * g);
+    const float d = half_bits_to_float(lds16(blk + 208));
     const float ds0 = d * static_cast<float>(static_cast<int>(static_cast<int8_t>(sc2 & 0xFFu)));
     const float ds1 = d * static_cast<float>(static_cast<int>(static_cast<int8_t>(sc2 >> 8)));
     const int sl = 4 * ((g & 3) >> 1);
@@ -195,15 +214,14 @@ __device__ __forceinline__ void decode32<QT_Q6_K>(const uint8_t* blk, int g, con
 }
 
 template <>
-__device__ __forceinline__ void decode32<QT_Q3_K>(const uint8_t* blk, int g, const uint64_t*,
-                                                  uint4 (&out)[4]) {
+__device__ __forceinline__ void decode32<QT_Q3_K>(uint32_t blk, int g, uint32_t, uint4 (&out)[4]) {
     // weights i = 32g + j: low 2 bits qs[(g>>2)*32 + j] >> 2*(g&3); hmask[j] bit g set means
     // "do not subtract 4"; 6-bit scale (minus 32) per 16 weights.
     uint32_t hm[8], qs[8], s[3];
     ld_words<8>(blk, hm);
     ld_words<8>(blk + 32 + (g >> 2) * 32, qs);
     ld_words<3>(blk + 96, s);
-    const float d = half_bits_to_float(ld_u16(blk + 108));
+    const float d = half_bits_to_float(lds16(blk + 108));
     float ds[2];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
@@ -226,23 +244,22 @@ __device__ __forceinline__ void decode32<QT_Q3_K>(const uint8_t* blk, int g, con
 }
 
 template <>
-__device__ __forceinline__ void decode32<QT_IQ2_S>(const uint8_t* blk, int g, const uint64_t* grid,
-                                                   uint4 (&out)[4]) {
+__device__ __forceinline__ void decode32<QT_IQ2_S>(uint32_t blk, int g, uint32_t grid, uint4 (&out)[4]) {
     // weights 32g..32g+31 = codebook groups 4g..4g+3 of 8 weights: index qs[gg] | 2 bits of
     // qh[g] << 8, sign byte qs[32 + gg]; one 4-bit scale per 16 weights in scales[g].
     uint32_t idxw[1], sgnw[1];
     ld_words<1>(blk + 2 + 4 * g, idxw);
     ld_words<1>(blk + 34 + 4 * g, sgnw);
-    const uint32_t qh = blk[66 + g];
-    const uint32_t scb = blk[74 + g];
-    const float d = half_bits_to_float(ld_u16(blk));
+    const uint32_t qh = lds8(blk + 66 + g);
+    const uint32_t scb = lds8(blk + 74 + g);
+    const float d = half_bits_to_float(lds16(blk));
     const float db0 = (d * (0.5f + static_cast<float>(scb & 15u))) * 0.25f;
     const float db1 = (d * (0.5f + static_cast<float>(scb >> 4))) * 0.25f;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
         const uint32_t idx = ((idxw[0] >> (8 * c)) & 0xFFu) | (((qh >> (2 * c)) & 3u) << 8);
-        const uint64_t mags = grid[idx];
-        const uint32_t m0 = static_cast<uint32_t>(mags), m1 = static_cast<uint32_t>(mags >> 32);
+        const uint2 mags = lds64(grid + idx * 8);
+        const uint32_t m0 = mags.x, m1 = mags.y;
         const uint32_t sg = (sgnw[0] >> (8 * c)) & 0xFFu;
         const float db = c < 2 ? db0 : db1;
         const uint32_t dbb = __float_as_uint(db);

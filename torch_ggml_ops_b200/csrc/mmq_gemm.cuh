@@ -146,18 +146,14 @@ __device__ __forceinline__ bool lane0_wait(uint32_t bar, uint32_t parity, volati
     if (lane == 0) ok = mbar_wait(bar, parity, abort_word, code) ? 1 : 0;
     return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
 }
-// Every lane waits (each needs the acquire), the warp agrees on the outcome.
+// Every lane waits (each needs the acquire), the warp agrees on the outcome.  The common case -
+// the phase has already completed - costs one try_wait and one vote.
 __device__ __forceinline__ bool all_wait(uint32_t bar, uint32_t parity, volatile int* abort_word,
                                          int code) {
-#ifdef TGO_EXP_LOWPOLL
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_word, code) ? 1 : 0;
-    __syncwarp();
-    return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
-#else
-    const bool ok = mbar_wait(bar, parity, abort_word, code);
+    bool ok = mbar_try_wait(bar, parity);
+    if (__all_sync(0xFFFFFFFFu, ok)) return true;
+    if (!ok) ok = mbar_wait(bar, parity, abort_word, code);
     return __all_sync(0xFFFFFFFFu, ok) != 0;
-#endif
 }
 
 // Optional per-role cycle accounting (compile with -DTGO_ROLE_TIMERS): CTA 0 prints, for one lane
@@ -205,7 +201,6 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     static_assert(kBarBytes + 16 <= 512, "misc region");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc_g + kBarBytes);
     volatile int* abort_word = reinterpret_cast<volatile int*>(misc_g + kBarBytes + 4);
-    const uint64_t* grid = reinterpret_cast<const uint64_t*>(grid_g);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -259,13 +254,13 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 for (int step = 0; step < nsteps; ++step, ++it) {
                     const uint32_t s = it % NB, ph = (it / NB) & 1u;
                     if (!TGO_TIMED(tw0, lane0_wait(bar_act_empty + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty, lane))) { ok = false; break; }
+#ifdef TGO_ROLE_TIMERS
+                    const long long t_a0 = clock64();
+#endif
                     if (lane == 0) {
                         const int set = MODE == kFwd ? 0 : step / steps_set;
                         const int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
                         const uint32_t bar = bar_act_full + 8 * s;
-#ifdef TGO_EXP_NO_ACT
-                        mbar_arrive(bar);
-#else
                         mbar_arrive_expect_tx(bar, static_cast<uint32_t>(t.ntok_pad) * 128u);
                         uint32_t dst = act_s + s * kActTileBytes;
                         int row = t.row0, rem = t.ntok_pad;
@@ -279,10 +274,19 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                                 rem -= h;
                             }
                         }
-#endif
                     }
+#ifdef TGO_ROLE_TIMERS
+                    const long long t_a1 = clock64();
+                    tw1 += t_a1 - t_a0;
+#endif
                     __syncwarp();
+#ifdef TGO_ROLE_TIMERS
+                    tw2 += clock64() - t_a1;
+#endif
                 }
+#ifdef TGO_ROLE_TIMERS
+                twork += 1;
+#endif
             }
         } else {
             // Rows whose byte length is not a multiple of 16 cannot be described to TMA: copy
@@ -350,9 +354,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                         const uint64_t adesc = MODE == kFwd ? umma_smem_desc(wa + kk * 32, 16, 1024)
                                                             : umma_smem_desc(wa + kk * 2048, 8192, 1024);
                         const uint64_t bdesc = umma_smem_desc(ba + kk * 32, 16, 1024);
-#ifndef TGO_EXP_NO_MMA
                         umma_bf16(d_tmem, adesc, bdesc, idesc, (step | kk) != 0 ? 1u : 0u);
-#endif
                     }
 #ifdef TGO_ROLE_TIMERS
                     const long long t_i1 = clock64();
@@ -396,15 +398,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     }
                     const long long g0 = static_cast<long long>(t.expert) * N + n_first;  // first global weight row
                     const uint32_t bar = bar_raw_full + 8 * r;
-#ifdef TGO_EXP_NO_RAW
-                    mbar_arrive(bar);
-                    const uint32_t stage_s = raw_s + r * Cfg::kRawStageBytes;
-                    for (int c = 0; c < 0; ++c) {
-#else
                     mbar_arrive_expect_tx(bar, static_cast<uint32_t>(kRows) * Fmt::kCopy);
                     const uint32_t stage_s = raw_s + r * Cfg::kRawStageBytes;
                     for (int c = 0; c < P; ++c) {
-#endif
                         // first row of class c at or after g0, as a row index inside map c
                         const long long first = g0 + ((c - g0) & (P - 1));
                         const int y = static_cast<int>((first - c) >> lgP);
@@ -418,92 +414,105 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         }
     } else if (warp >= kFirstDecodeWarp && warp < kFirstEpilogueWarp) {
         // ------------------------------------------------------------ decode warps
-        // Group g decodes the steps whose running index is g (mod kDecodeGroups).  Forward: one raw
-        // stage (a super-block column) serves four steps, two per group; backward: one per step.
+        // Group g decodes the steps whose running index is g (mod kDecodeGroups); both groups and
+        // the UMMA issuer walk the decoded-weight ring in running-step order.  Forward: one raw
+        // stage (a super-block column of 128 rows) serves four steps, two per group; a thread
+        // keeps its row and 32-weight half for the whole tile.  Backward: one raw stage (64 rows)
+        // per step; a thread keeps its row slot and 32-weight group.
         const int group = (warp - kFirstDecodeWarp) / kDecodeWarps;
         const int dt = threadIdx.x - (kFirstDecodeWarp + group * kDecodeWarps) * 32;  // 0..255
-        uint32_t ita = 0, itr = 0;
+        const int row = MODE == kFwd ? dt >> 1 : dt >> 2;     // weight row inside the raw stage
+        const int sub = MODE == kFwd ? dt & 1 : dt & 3;       // which 32 weights of the step's span
+        // byte offsets of this thread's four 16-byte chunks inside a decoded tile (128B swizzle)
+        uint32_t coff[4];
+        {
+            const uint32_t base = (MODE == kFwd ? 0u : static_cast<uint32_t>(sub >> 1) * 8192u) + row * 128u;
+            const int cbase = 4 * (sub & 1);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) coff[c] = base + (((cbase + c) ^ (row & 7)) << 4);
+        }
+        const uint32_t grid_s = misc_s - kEpiStageBytes - Cfg::kGridBytes;
+        const int P = args.wgt_classes, lgP = args.wgt_classes_log2;
+        uint32_t sa = static_cast<uint32_t>(group) % NA, pa = (static_cast<uint32_t>(group) / NA) & 1u;
+        uint32_t raw_it = 0;       // forward: raw stages consumed; backward: running step index of the tile start
+        uint32_t parity_in = 0;    // parity of the running step index at the start of the tile
         bool ok = true;
         for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
             TileInfo t;
             if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
-            for (int step = 0; step < nsteps; ++step, ++ita) {
-                int row, g, n, kb;
-                uint32_t dst_off;  // byte offset of this thread's first chunk row inside the tile
-                int cbase;         // first 16-byte chunk index (0 or 4) in the 128-byte row
-                if (MODE == kFwd) {
-                    row = dt >> 1;
-                    const int half = dt & 1;
-                    kb = step >> 2;
-                    g = 2 * (step & 3) + half;
-                    n = t.m0 + row;
-                    dst_off = row * 128;
-                    cbase = 4 * half;
-                } else {
-                    row = dt >> 2;
-                    const int q = dt & 3;
-                    const int set = step / steps_set;
-                    kb = t.m0 >> 8;
-                    g = ((t.m0 >> 7) & 1) * 4 + q;
-                    n = (step - set * steps_set) * kStepK + row;
-                    dst_off = (q >> 1) * 8192 + row * 128;
-                    cbase = 4 * (q & 1);
+            // alignment class of the first weight row of a raw stage (0 for 16-byte-aligned formats)
+            const long long gexp = static_cast<long long>(t.expert) * N;
+            if (MODE == kFwd) {
+                const bool row_ok = t.m0 + row < N;
+                int slot = row, cls = 0;
+                if (!Fmt::kAligned) {
+                    cls = static_cast<int>((gexp + t.m0 + row) & (P - 1));
+                    slot = cls * (Cfg::kRawRows >> lgP) + (row >> lgP);
                 }
-                const uint32_t r = itr % NR, rph = (itr / NR) & 1u;
-                // forward: steps 4b..4b+3 share raw stage b; this group touches steps g and g+2 of them
-                const bool first_use = MODE == kFwd ? (step & 3) == group : true;
-                const bool last_use = MODE == kFwd ? (step & 3) == group + 2 : true;
-                const bool stage_done = MODE == kFwd ? (step & 3) == 3 : true;
-                if (static_cast<int>(ita % kDecodeGroups) != group) {
-                    if (stage_done) ++itr;
-                    continue;
-                }
-                if (first_use) {
-                    if (!TGO_TIMED(tw0, all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull))) { ok = false; break; }
-                }
-                const uint32_t sa = ita % NA, pa = (ita / NA) & 1u;
-                if (!TGO_TIMED(tw1, all_wait(bar_wgt_empty + 8 * sa, pa ^ 1u, abort_word, kAbortWgtEmpty))) { ok = false; break; }
-#ifdef TGO_ROLE_TIMERS
-                const long long t_dec0 = clock64();
-#endif
-                uint4 o[4];
-#ifdef TGO_EXP_NO_DECODE
-                if (false) {
-#else
-                if (n < N) {
-#endif
-                    // where the raw producer put this row: class (alignment of the global row), then row / P
-                    int slot = row, mis = 0;
-                    if (!Fmt::kAligned) {
-                        const int P = args.wgt_classes, lgP = args.wgt_classes_log2;
-                        const int c0 = static_cast<int>((static_cast<long long>(t.expert) * N + (n - row)) & (P - 1));
-                        const int cls = (c0 + row) & (P - 1);
-                        slot = cls * (Cfg::kRawRows >> lgP) + (row >> lgP);
-                        mis = (((cls * args.wgt_row_bytes) & 15) + kb * Fmt::kBytes) & 15;
-                    }
-                    const uint8_t* blk = raw_g + r * Cfg::kRawStageBytes + slot * Fmt::kCopy + mis;
-                    decode32<QT>(blk, g, grid, o);
-                } else {
-                    o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
-                }
-#ifdef TGO_ROLE_TIMERS
-                const long long t_dec1 = clock64();
-                twork2 += t_dec1 - t_dec0;
-#endif
-                uint8_t* tile_g = wgt_g + sa * kWgtTileBytes + dst_off;
+                const uint32_t blk0 = raw_s + slot * Fmt::kCopy;
+                const int mis0 = Fmt::kAligned ? 0 : (cls * args.wgt_row_bytes) & 15;
+                for (int kb = 0; kb < nkb && ok; ++kb, ++raw_it) {
+                    const uint32_t r = raw_it % NR, rph = (raw_it / NR) & 1u;
+                    if (!all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull)) { ok = false; break; }
+                    const uint32_t blk = blk0 + r * Cfg::kRawStageBytes + (Fmt::kAligned ? 0 : (mis0 + kb * Fmt::kBytes) & 15);
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    *reinterpret_cast<uint4*>(tile_g + (((cbase + c) ^ (row & 7)) << 4)) = o[c];
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(bar_wgt_full + 8 * sa);
-                    if (last_use) mbar_arrive(bar_raw_empty + 8 * r);
+                    for (int u = 0; u < 2; ++u) {
+                        if (!all_wait(bar_wgt_empty + 8 * sa, pa ^ 1u, abort_word, kAbortWgtEmpty)) { ok = false; break; }
+                        uint4 o[4];
+                        if (row_ok) {
+                            decode32<QT>(blk, 2 * (group + 2 * u) + sub, grid_s, o);
+                        } else {
+                            o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
+                        }
+                        const uint32_t tile_s = wgt_s + sa * kWgtTileBytes;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) sts128(tile_s + coff[c], o[c]);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            mbar_arrive(bar_wgt_full + 8 * sa);
+                            if (u == 1) mbar_arrive(bar_raw_empty + 8 * r);
+                        }
+                        sa += kDecodeGroups;
+                        if (sa >= NA) { sa -= NA; pa ^= 1u; }
+                    }
                 }
-#ifdef TGO_ROLE_TIMERS
-                twork += clock64() - t_dec0;
-#endif
-                if (stage_done) ++itr;
+            } else {
+                const int g = ((t.m0 >> 7) & 1) * 4 + sub;
+                const int kb = t.m0 >> 8;
+                for (int step = (group ^ parity_in) & 1; step < nsteps; step += kDecodeGroups) {
+                    const uint32_t it = raw_it + step;
+                    const uint32_t r = it % NR, rph = (it / NR) & 1u;
+                    if (!all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull)) { ok = false; break; }
+                    if (!all_wait(bar_wgt_empty + 8 * sa, pa ^ 1u, abort_word, kAbortWgtEmpty)) { ok = false; break; }
+                    const int set = step >= steps_set ? 1 : 0;
+                    const int n_first = (step - set * steps_set) * kStepK;
+                    uint4 o[4];
+                    if (n_first + row < N) {
+                        int slot = row, mis = 0;
+                        if (!Fmt::kAligned) {
+                            const int cls = static_cast<int>((gexp + n_first + row) & (P - 1));
+                            slot = cls * (Cfg::kRawRows >> lgP) + (row >> lgP);
+                            mis = (((cls * args.wgt_row_bytes) & 15) + kb * Fmt::kBytes) & 15;
+                        }
+                        decode32<QT>(raw_s + r * Cfg::kRawStageBytes + slot * Fmt::kCopy + mis, g, grid_s, o);
+                    } else {
+                        o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    const uint32_t tile_s = wgt_s + sa * kWgtTileBytes;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) sts128(tile_s + coff[c], o[c]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(bar_wgt_full + 8 * sa);
+                        mbar_arrive(bar_raw_empty + 8 * r);
+                    }
+                    sa += kDecodeGroups;
+                    if (sa >= NA) { sa -= NA; pa ^= 1u; }
+                }
+                raw_it += nsteps;
+                parity_in = raw_it & 1u;
             }
         }
     } else if (warp >= kFirstEpilogueWarp) {

@@ -42,6 +42,9 @@ static int cuda_fail(cudaError_t e, const char* what) {
     return fail(TGO_E_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
 }
 
+// Error setter for the other translation units of the library.
+int route_fail(int code, const char* msg) { return fail(code, "%s", msg); }
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int num_sms() {
@@ -242,7 +245,7 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
     if (blk >= n_blocks) return;
     const int mis = static_cast<int>((blk * Fmt::kBytes) & 15);
     uint4 o[4];
-    decode32<QT>(windows + b * Fmt::kSlot + mis, g, grid_s, o);
+    decode32<QT>(smem_u32(windows) + b * Fmt::kSlot + mis, g, smem_u32(grid_s), o);
     uint4* dst = reinterpret_cast<uint4*>(out + blk * 256 + g * 32);
 #pragma unroll
     for (int c = 0; c < 4; ++c) dst[c] = o[c];

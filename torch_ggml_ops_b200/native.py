@@ -28,6 +28,11 @@ SIGNATURES = {
     "tgo_build_tiles": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tgo_grouped_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
     "tgo_grouped_dx": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
+    "tgo_route_workspace_bytes": (_i64, [_i64, _i64]),
+    "tgo_route_sort": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "tgo_gather_rows": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _vp]),
+    "tgo_combine_rows": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "tgo_quantize_q8": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     "tgo_grouped_fwd_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
 }
 
@@ -134,3 +139,51 @@ def grouped_fwd_noalloc(x, w0, w1, y0, y1, expert_indices, expert_offsets, num_e
                                         _ptr(expert_offsets), expert_indices.numel(), num_experts, rows,
                                         out_features, in_features, quant_type, _stream(stream)),
           "tgo_grouped_fwd_noalloc")
+
+
+def route_sort(expert_ids, num_experts, stream=None):
+    """Device counting sort of routed pairs by expert.  ``expert_ids``: int32 [n_pairs] on the GPU.
+    Returns (sorted_to_pair, pair_to_sorted, expert_indices int64 [E], expert_offsets int32 [E])."""
+    import torch
+
+    n = expert_ids.numel()
+    dev = expert_ids.device
+    s2p = torch.empty(n, dtype=torch.int32, device=dev)
+    p2s = torch.empty(n, dtype=torch.int32, device=dev)
+    ei = torch.empty(num_experts, dtype=torch.int64, device=dev)
+    eo = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    ws = torch.empty(lib().tgo_route_workspace_bytes(n, num_experts), dtype=torch.uint8, device=dev)
+    check(lib().tgo_route_sort(_ptr(expert_ids), n, num_experts, _ptr(s2p), _ptr(p2s), _ptr(ei), _ptr(eo), _ptr(ws),
+                               ws.numel(), _stream(stream)), "tgo_route_sort")
+    return s2p, p2s, ei, eo
+
+
+def gather_rows(src, index, divisor=1, stream=None):
+    import torch
+
+    dst = torch.empty((index.numel(), src.shape[1]), dtype=src.dtype, device=src.device)
+    check(lib().tgo_gather_rows(_ptr(src), _ptr(index), divisor, _ptr(dst), index.numel(), src.shape[1],
+                                _stream(stream)), "tgo_gather_rows")
+    return dst
+
+
+def combine_rows(rows, pair_to_sorted, top_k, weights=None, stream=None):
+    import torch
+
+    tokens = pair_to_sorted.numel() // top_k
+    out = torch.empty((tokens, rows.shape[1]), dtype=rows.dtype, device=rows.device)
+    check(lib().tgo_combine_rows(_ptr(rows), _ptr(pair_to_sorted), _ptr(weights), _ptr(out), tokens, top_k,
+                                 rows.shape[1], _stream(stream)), "tgo_combine_rows")
+    return out
+
+
+def quantize_q8(x, stream=None):
+    """bf16 [rows, width] -> (int8 [rows, width], fp32 d [rows, width/32], fp32 sum [rows, width/32])."""
+    import torch
+
+    rows, width = x.shape
+    q = torch.empty((rows, width), dtype=torch.int8, device=x.device)
+    d = torch.empty((rows, width // 32), dtype=torch.float32, device=x.device)
+    s = torch.empty((rows, width // 32), dtype=torch.float32, device=x.device)
+    check(lib().tgo_quantize_q8(_ptr(x), rows, width, _ptr(q), _ptr(d), _ptr(s), _stream(stream)), "tgo_quantize_q8")
+    return q, d, s
