@@ -19,13 +19,20 @@
 // Warp roles (768 threads): 0 activation producer (TMA), 1 UMMA issuer + TMEM owner, 2 raw
 // weight producer (TMA), 3 idle, 4-19 decode (two groups of 8 warps on alternate steps), 20-23
 // epilogue (TMEM -> bf16 -> global).
+//
+// Synchronisation per 64-element step i (running index over all tiles of the CTA):
+//   full[i % NB]  <- the activation TMA (expect_tx) and the 8 decode warps of the step's group;
+//                    the UMMA issuer waits on it once and issues the step's four UMMAs;
+//   done[i % NB]  <- one tcgen05.commit after those UMMAs; the activation producer waits on it
+//                    before refilling the slot, the decode group of step i + NA waits on it before
+//                    overwriting decoded-weight stage i % NA (NA <= NB);
+//   raw_full / raw_empty: TMA raw-block ring <-> decode;  acc_full / acc_empty: TMEM <-> epilogue.
 // All waits are bounded (ptx.cuh); a wait that gives up unwinds every role to the common exit,
 // which frees TMEM and records a status code.
 #pragma once
 
 #include "gguf_decode.cuh"
 #include "ptx.cuh"
-#include <cstdio>
 
 namespace tgo {
 
@@ -156,22 +163,13 @@ __device__ __forceinline__ bool all_wait(uint32_t bar, uint32_t parity, volatile
     return __all_sync(0xFFFFFFFFu, ok) != 0;
 }
 
-// Optional per-role cycle accounting (compile with -DTGO_ROLE_TIMERS): CTA 0 prints, for one lane
-// of each role, the cycles spent in each wait and in its own work.  Off in the product build.
-#ifdef TGO_ROLE_TIMERS
-#define TGO_T0() const long long tgo_t0_ = clock64()
-#define TGO_ACC(var) var += clock64() - tgo_t0_
-#define TGO_TIMED(var, expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); var += clock64() - t_; return r_; }()
-#else
-#define TGO_TIMED(var, expr) (expr)
-#endif
-
 template <int QT, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     using Cfg = GemmCfg<QT, MODE>;
     using Fmt = BlockFmt<QT>;
     constexpr int NA = Cfg::kWgtStages, NB = kActStages, NR = Cfg::kRawStages;
+    static_assert(NA <= NB, "the decoded-weight ring may not be deeper than the step ring");
 
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -181,32 +179,27 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     const uint32_t act_s = smem_base;
     const uint32_t wgt_s = act_s + NB * kActTileBytes;
     const uint32_t raw_s = wgt_s + NA * kWgtTileBytes;
+    const uint32_t grid_s = raw_s + Cfg::kRawBytes + 128;
+    const uint32_t epi_s = grid_s + Cfg::kGridBytes;
+    const uint32_t misc_s = epi_s + kEpiStageBytes;
     uint8_t* act_g = smem;
-    uint8_t* wgt_g = act_g + NB * kActTileBytes;
-    uint8_t* raw_g = wgt_g + NA * kWgtTileBytes;
-    uint8_t* grid_g = raw_g + Cfg::kRawBytes + 128;
-    uint8_t* epi_g = grid_g + Cfg::kGridBytes;
-    uint8_t* misc_g = epi_g + kEpiStageBytes;
-    const uint32_t misc_s = raw_s + Cfg::kRawBytes + 128 + Cfg::kGridBytes + kEpiStageBytes;
+    uint8_t* grid_g = smem + (grid_s - smem_base);
+    uint8_t* epi_g = smem + (epi_s - smem_base);
+    uint8_t* misc_g = smem + (misc_s - smem_base);
     // barriers (8 bytes each)
-    const uint32_t bar_act_full = misc_s;                    // NB
-    const uint32_t bar_act_empty = bar_act_full + 8 * NB;    // NB
-    const uint32_t bar_wgt_full = bar_act_empty + 8 * NB;    // NA
-    const uint32_t bar_wgt_empty = bar_wgt_full + 8 * NA;    // NA
-    const uint32_t bar_raw_full = bar_wgt_empty + 8 * NA;    // NR
+    const uint32_t bar_full = misc_s;                        // NB
+    const uint32_t bar_done = bar_full + 8 * NB;             // NB
+    const uint32_t bar_raw_full = bar_done + 8 * NB;         // NR
     const uint32_t bar_raw_empty = bar_raw_full + 8 * NR;    // NR
     const uint32_t bar_acc_full = bar_raw_empty + 8 * NR;    // 2
     const uint32_t bar_acc_empty = bar_acc_full + 16;        // 2
-    constexpr int kBarBytes = 8 * (2 * NB + 2 * NA + 2 * NR + 4);
+    constexpr int kBarBytes = 8 * (2 * NB + 2 * NR + 4);
     static_assert(kBarBytes + 16 <= 512, "misc region");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc_g + kBarBytes);
     volatile int* abort_word = reinterpret_cast<volatile int*>(misc_g + kBarBytes + 4);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    long long tw0 = 0, tw1 = 0, tw2 = 0, twork = 0, twork2 = 0;  // role timers (unused unless TGO_ROLE_TIMERS)
-    (void)tw0; (void)tw1; (void)tw2; (void)twork; (void)twork2;
-    const long long t_kernel0 = clock64();
 
     const int N = args.out_features, K = args.in_features;
     const int nkb = K >> 8;
@@ -219,9 +212,11 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     const long long total_tiles = static_cast<long long>(ntasks) * mtiles;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NB; ++i) { mbar_init(bar_act_full + 8 * i, 1); mbar_init(bar_act_empty + 8 * i, 1); }
-        for (int i = 0; i < NA; ++i) { mbar_init(bar_wgt_full + 8 * i, kDecodeWarps); mbar_init(bar_wgt_empty + 8 * i, 1); }
-        for (int i = 0; i < NR; ++i) { mbar_init(bar_raw_full + 8 * i, 1); mbar_init(bar_raw_empty + 8 * i, MODE == kFwd ? kDecodeWarps * kDecodeGroups : kDecodeWarps); }
+        for (int i = 0; i < NB; ++i) { mbar_init(bar_full + 8 * i, 1 + kDecodeWarps); mbar_init(bar_done + 8 * i, 1); }
+        for (int i = 0; i < NR; ++i) {
+            mbar_init(bar_raw_full + 8 * i, 1);
+            mbar_init(bar_raw_empty + 8 * i, MODE == kFwd ? kDecodeWarps * kDecodeGroups : kDecodeWarps);
+        }
         for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, 4); }
         *abort_word = 0;
         mbar_fence_init();
@@ -245,22 +240,17 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             if (lane == 0) {
                 for (int s = 0; s < args.nsets; ++s)
                     for (int b = 0; b < kNumBoxes; ++b) prefetch_tmap(&args.act_maps[s].box[b]);
-            }
-            uint32_t it = 0;
-            bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                TileInfo t;
-                if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
-                for (int step = 0; step < nsteps; ++step, ++it) {
-                    const uint32_t s = it % NB, ph = (it / NB) & 1u;
-                    if (!TGO_TIMED(tw0, lane0_wait(bar_act_empty + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty, lane))) { ok = false; break; }
-#ifdef TGO_ROLE_TIMERS
-                    const long long t_a0 = clock64();
-#endif
-                    if (lane == 0) {
+                uint32_t it = 0;
+                bool ok = true;
+                for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                    TileInfo t;
+                    if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+                    for (int step = 0; step < nsteps; ++step, ++it) {
+                        const uint32_t s = it % NB, ph = (it / NB) & 1u;
+                        if (!mbar_wait(bar_done + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty)) { ok = false; break; }
                         const int set = MODE == kFwd ? 0 : step / steps_set;
                         const int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
-                        const uint32_t bar = bar_act_full + 8 * s;
+                        const uint32_t bar = bar_full + 8 * s;
                         mbar_arrive_expect_tx(bar, static_cast<uint32_t>(t.ntok_pad) * 128u);
                         uint32_t dst = act_s + s * kActTileBytes;
                         int row = t.row0, rem = t.ntok_pad;
@@ -275,18 +265,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                             }
                         }
                     }
-#ifdef TGO_ROLE_TIMERS
-                    const long long t_a1 = clock64();
-                    tw1 += t_a1 - t_a0;
-#endif
-                    __syncwarp();
-#ifdef TGO_ROLE_TIMERS
-                    tw2 += clock64() - t_a1;
-#endif
                 }
-#ifdef TGO_ROLE_TIMERS
-                twork += 1;
-#endif
             }
         } else {
             // Rows whose byte length is not a multiple of 16 cannot be described to TMA: copy
@@ -299,7 +278,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
                 for (int step = 0; step < nsteps; ++step, ++it) {
                     const uint32_t s = it % NB, ph = (it / NB) & 1u;
-                    if (!lane0_wait(bar_act_empty + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty, lane)) { ok = false; break; }
+                    if (!lane0_wait(bar_done + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty, lane)) { ok = false; break; }
                     const int set = MODE == kFwd ? 0 : step / steps_set;
                     const int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
                     const __nv_bfloat16* src = args.act[set];
@@ -319,36 +298,38 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_act_full + 8 * s);
+                    if (lane == 0) mbar_arrive(bar_full + 8 * s);
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ UMMA issuer
-        uint32_t ita = 0, itb = 0, tl = 0;
-        bool ok = true;
-        for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-            TileInfo t;
-            if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
-            const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
-            ++tl;
-            if (!TGO_TIMED(tw2, lane0_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kAbortAccEmpty, lane))) break;
-            tc_fence_after_sync();
-            const uint32_t d_tmem = tmem_base + acc * kTileTok;
-            const uint32_t idesc =
-                umma_idesc_bf16(static_cast<uint32_t>(t.ntok_pad), MODE == kBwd ? 1u : 0u, 0u);
-            for (int step = 0; step < nsteps; ++step, ++ita, ++itb) {
-                const uint32_t sa = ita % NA, pa = (ita / NA) & 1u;
-                const uint32_t sb = itb % NB, pb = (itb / NB) & 1u;
-                if (!TGO_TIMED(tw0, lane0_wait(bar_wgt_full + 8 * sa, pa, abort_word, kAbortWgtFull, lane))) { ok = false; break; }
-                if (!TGO_TIMED(tw1, lane0_wait(bar_act_full + 8 * sb, pb, abort_word, kAbortActFull, lane))) { ok = false; break; }
-                if (lane == 0) {
-#ifdef TGO_ROLE_TIMERS
-                    const long long t_i0 = clock64();
-#endif
+        // ------------------------------------------------------------ UMMA issuer (one thread)
+        if (lane == 0) {
+            uint32_t it = 0, tl = 0;
+            bool ok = true;
+            // the test of the next step's barrier is issued before this step's UMMAs, so its latency
+            // overlaps their issue; a negative answer only means "ask again, blocking"
+            bool ready = false;
+            for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                TileInfo t;
+                if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+                const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
+                ++tl;
+                if (!mbar_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kAbortAccEmpty)) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * kTileTok;
+                const uint32_t idesc =
+                    umma_idesc_bf16(static_cast<uint32_t>(t.ntok_pad), MODE == kBwd ? 1u : 0u, 0u);
+                for (int step = 0; step < nsteps; ++step, ++it) {
+                    const uint32_t s = it % NB, ph = (it / NB) & 1u;
+                    if (!ready && !mbar_wait(bar_full + 8 * s, ph, abort_word, kAbortWgtFull)) { ok = false; break; }
+                    {
+                        const uint32_t nx = it + 1;
+                        ready = mbar_try_wait(bar_full + 8 * (nx % NB), (nx / NB) & 1u);
+                    }
                     tc_fence_after_sync();
-                    const uint32_t wa = wgt_s + sa * kWgtTileBytes;
-                    const uint32_t ba = act_s + sb * kActTileBytes;
+                    const uint32_t wa = wgt_s + (it % NA) * kWgtTileBytes;
+                    const uint32_t ba = act_s + s * kActTileBytes;
 #pragma unroll
                     for (int kk = 0; kk < kStepK / 16; ++kk) {
                         const uint64_t adesc = MODE == kFwd ? umma_smem_desc(wa + kk * 32, 16, 1024)
@@ -356,40 +337,28 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                         const uint64_t bdesc = umma_smem_desc(ba + kk * 32, 16, 1024);
                         umma_bf16(d_tmem, adesc, bdesc, idesc, (step | kk) != 0 ? 1u : 0u);
                     }
-#ifdef TGO_ROLE_TIMERS
-                    const long long t_i1 = clock64();
-                    twork += t_i1 - t_i0;
-#endif
-                    umma_commit(bar_wgt_empty + 8 * sa);
-                    umma_commit(bar_act_empty + 8 * sb);
-#ifdef TGO_ROLE_TIMERS
-                    twork2 += clock64() - t_i1;
-#endif
+                    umma_commit(bar_done + 8 * s);
                 }
-                __syncwarp();
+                if (ok) umma_commit(bar_acc_full + 8 * acc);
             }
-            if (ok && lane == 0) umma_commit(bar_acc_full + 8 * acc);
-            __syncwarp();
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------ raw weight producer
         // One box load per alignment class and stage: rows / P block windows of kCopy bytes each.
-        uint32_t itr = 0;
-        bool ok = true;
-        const int P = args.wgt_classes, lgP = args.wgt_classes_log2;
-        constexpr int kRows = Cfg::kRawRows;
         if (lane == 0) {
+            uint32_t itr = 0;
+            bool ok = true;
+            const int P = args.wgt_classes, lgP = args.wgt_classes_log2;
+            constexpr int kRows = Cfg::kRawRows;
             for (int s = 0; s < args.nsets; ++s)
                 for (int c = 0; c < P; ++c) prefetch_tmap(&args.wgt_maps[s].cls[c]);
-        }
-        for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-            TileInfo t;
-            if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
-            const int nraw = MODE == kFwd ? nkb : nsteps;
-            for (int ri = 0; ri < nraw; ++ri, ++itr) {
-                const uint32_t r = itr % NR, ph = (itr / NR) & 1u;
-                if (!TGO_TIMED(tw0, lane0_wait(bar_raw_empty + 8 * r, ph ^ 1u, abort_word, kAbortRawEmpty, lane))) { ok = false; break; }
-                if (lane == 0) {
+            for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                TileInfo t;
+                if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+                const int nraw = MODE == kFwd ? nkb : nsteps;
+                for (int ri = 0; ri < nraw; ++ri, ++itr) {
+                    const uint32_t r = itr % NR, ph = (itr / NR) & 1u;
+                    if (!mbar_wait(bar_raw_empty + 8 * r, ph ^ 1u, abort_word, kAbortRawEmpty)) { ok = false; break; }
                     int set, n_first, kb;
                     if (MODE == kFwd) {
                         set = t.set; n_first = t.m0; kb = ri;
@@ -409,13 +378,11 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                         tma_load_2d(stage_s + c * (kRows >> lgP) * Fmt::kCopy, &args.wgt_maps[set].cls[c], bar, x, y);
                     }
                 }
-                __syncwarp();
             }
         }
     } else if (warp >= kFirstDecodeWarp && warp < kFirstEpilogueWarp) {
         // ------------------------------------------------------------ decode warps
-        // Group g decodes the steps whose running index is g (mod kDecodeGroups); both groups and
-        // the UMMA issuer walk the decoded-weight ring in running-step order.  Forward: one raw
+        // Group g decodes the steps whose running index is g (mod kDecodeGroups).  Forward: one raw
         // stage (a super-block column of 128 rows) serves four steps, two per group; a thread
         // keeps its row and 32-weight half for the whole tile.  Backward: one raw stage (64 rows)
         // per step; a thread keeps its row slot and 32-weight group.
@@ -431,16 +398,39 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) coff[c] = base + (((cbase + c) ^ (row & 7)) << 4);
         }
-        const uint32_t grid_s = misc_s - kEpiStageBytes - Cfg::kGridBytes;
         const int P = args.wgt_classes, lgP = args.wgt_classes_log2;
-        uint32_t sa = static_cast<uint32_t>(group) % NA, pa = (static_cast<uint32_t>(group) / NA) & 1u;
-        uint32_t raw_it = 0;       // forward: raw stages consumed; backward: running step index of the tile start
-        uint32_t parity_in = 0;    // parity of the running step index at the start of the tile
+        uint32_t it = static_cast<uint32_t>(group);  // running index of this group's next step
+        uint32_t raw_it = 0;   // forward: raw stages consumed; backward: running step index at the tile start
         bool ok = true;
+
+        // waits until decoded-weight stage (it % NA) is free, decodes into it and signals the step
+        auto emit = [&](uint32_t blk, int g, bool valid, uint32_t raw_bar_to_release) -> bool {
+            if (it >= static_cast<uint32_t>(NA)) {
+                const uint32_t j = it - NA;  // the step that last used this stage
+                if (!all_wait(bar_done + 8 * (j % NB), (j / NB) & 1u, abort_word, kAbortWgtEmpty)) return false;
+            }
+            uint4 o[4];
+            if (valid) {
+                decode32<QT>(blk, g, grid_s, o);
+            } else {
+                o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            const uint32_t tile_s = wgt_s + (it % NA) * kWgtTileBytes;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) sts128(tile_s + coff[c], o[c]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_full + 8 * (it % NB));
+                if (raw_bar_to_release != 0) mbar_arrive(raw_bar_to_release);
+            }
+            it += kDecodeGroups;
+            return true;
+        };
+
         for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
             TileInfo t;
             if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
-            // alignment class of the first weight row of a raw stage (0 for 16-byte-aligned formats)
             const long long gexp = static_cast<long long>(t.expert) * N;
             if (MODE == kFwd) {
                 const bool row_ok = t.m0 + row < N;
@@ -457,62 +447,33 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     const uint32_t blk = blk0 + r * Cfg::kRawStageBytes + (Fmt::kAligned ? 0 : (mis0 + kb * Fmt::kBytes) & 15);
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
-                        if (!all_wait(bar_wgt_empty + 8 * sa, pa ^ 1u, abort_word, kAbortWgtEmpty)) { ok = false; break; }
-                        uint4 o[4];
-                        if (row_ok) {
-                            decode32<QT>(blk, 2 * (group + 2 * u) + sub, grid_s, o);
-                        } else {
-                            o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
-                        }
-                        const uint32_t tile_s = wgt_s + sa * kWgtTileBytes;
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) sts128(tile_s + coff[c], o[c]);
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0) {
-                            mbar_arrive(bar_wgt_full + 8 * sa);
-                            if (u == 1) mbar_arrive(bar_raw_empty + 8 * r);
-                        }
-                        sa += kDecodeGroups;
-                        if (sa >= NA) { sa -= NA; pa ^= 1u; }
+                        if (!emit(blk, 2 * (group + 2 * u) + sub, row_ok, u == 1 ? bar_raw_empty + 8 * r : 0u)) { ok = false; break; }
                     }
                 }
             } else {
                 const int g = ((t.m0 >> 7) & 1) * 4 + sub;
                 const int kb = t.m0 >> 8;
-                for (int step = (group ^ parity_in) & 1; step < nsteps; step += kDecodeGroups) {
-                    const uint32_t it = raw_it + step;
-                    const uint32_t r = it % NR, rph = (it / NR) & 1u;
+                // this group's first step of the tile: running index parity must equal the group
+                for (int step = static_cast<int>((it - raw_it) & 0x7FFFFFFFu); step < nsteps; step += kDecodeGroups) {
+                    const uint32_t ri = raw_it + step;
+                    const uint32_t r = ri % NR, rph = (ri / NR) & 1u;
                     if (!all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull)) { ok = false; break; }
-                    if (!all_wait(bar_wgt_empty + 8 * sa, pa ^ 1u, abort_word, kAbortWgtEmpty)) { ok = false; break; }
                     const int set = step >= steps_set ? 1 : 0;
                     const int n_first = (step - set * steps_set) * kStepK;
-                    uint4 o[4];
-                    if (n_first + row < N) {
+                    const bool valid = n_first + row < N;
+                    uint32_t blk = 0;
+                    if (valid) {
                         int slot = row, mis = 0;
                         if (!Fmt::kAligned) {
                             const int cls = static_cast<int>((gexp + n_first + row) & (P - 1));
                             slot = cls * (Cfg::kRawRows >> lgP) + (row >> lgP);
                             mis = (((cls * args.wgt_row_bytes) & 15) + kb * Fmt::kBytes) & 15;
                         }
-                        decode32<QT>(raw_s + r * Cfg::kRawStageBytes + slot * Fmt::kCopy + mis, g, grid_s, o);
-                    } else {
-                        o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
+                        blk = raw_s + r * Cfg::kRawStageBytes + slot * Fmt::kCopy + mis;
                     }
-                    const uint32_t tile_s = wgt_s + sa * kWgtTileBytes;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) sts128(tile_s + coff[c], o[c]);
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(bar_wgt_full + 8 * sa);
-                        mbar_arrive(bar_raw_empty + 8 * r);
-                    }
-                    sa += kDecodeGroups;
-                    if (sa >= NA) { sa -= NA; pa ^= 1u; }
+                    if (!emit(blk, g, valid, bar_raw_empty + 8 * r)) { ok = false; break; }
                 }
                 raw_it += nsteps;
-                parity_in = raw_it & 1u;
             }
         }
     } else if (warp >= kFirstEpilogueWarp) {
@@ -525,10 +486,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
             const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
             ++tl;
-            if (!TGO_TIMED(tw0, all_wait(bar_acc_full + 8 * acc, aph, abort_word, kAbortAccFull))) break;
-#ifdef TGO_ROLE_TIMERS
-            const long long t_ep0 = clock64();
-#endif
+            if (!all_wait(bar_acc_full + 8 * acc, aph, abort_word, kAbortAccFull)) break;
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + acc * kTileTok + (static_cast<uint32_t>(quad * 32) << 16);
             const int mq = t.m0 + quad * 32;  // first output column of this warp
@@ -582,17 +540,11 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
-#ifdef TGO_ROLE_TIMERS
-            twork += clock64() - t_ep0;
-#endif
         }
     }
 
-#ifdef TGO_ROLE_TIMERS
-    if (blockIdx.x == 0 && lane == 0 && (warp <= 2 || warp == kFirstDecodeWarp || warp == kFirstDecodeWarp + kDecodeWarps || warp == kFirstEpilogueWarp))
-        printf("role warp %2d: wait0 %9lld wait1 %9lld wait2 %9lld work %9lld work2 %9lld total %9lld\n", warp, tw0, tw1, tw2, twork, twork2, clock64() - t_kernel0);
-#endif
     // ------------------------------------------------------------ common exit
+    __syncwarp();
     if (*abort_word != 0) {
         // Some wait gave up.  Give copies and UMMAs still in flight a bounded time to land before
         // shared memory and TMEM are released.
