@@ -39,6 +39,13 @@ class DispatchPlan:
     expert_offsets: torch.Tensor     # int32 [E_local] cumulative end rows in expert-major order
     rows_local: int                  # R_local
     rows_recv: int                   # R_recv
+    pair_to_sorted: torch.Tensor = None   # [R_local] inverse of send_perm
+    recv_inv: torch.Tensor = None         # [R_recv] inverse of recv_perm
+
+
+def _native_rows(t: torch.Tensor) -> bool:
+    """True when the hand-written gather / combine kernels apply (CUDA, bf16, 16-byte rows)."""
+    return t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.shape[1] % 8 == 0 and t.is_contiguous()
 
 
 class ExpertParallel:
@@ -61,9 +68,20 @@ class ExpertParallel:
             raise ValueError("topk_ids must have shape [tokens, top_k]")
         device = topk_ids.device
         W, EL = self.world, self.experts_per_rank
-        flat = topk_ids.reshape(-1).to(torch.int64)
-        send_perm = torch.argsort(flat, stable=True)
-        send_counts = torch.bincount(flat, minlength=self.num_experts).reshape(W, EL)
+        if topk_ids.is_cuda and self.num_experts <= 4096:
+            # device counting sort (routing.cu): permutation, its inverse and the per-expert ends
+            from . import native
+
+            flat = topk_ids.reshape(-1).to(torch.int32)
+            send_perm, pair_to_sorted, _, ends = native.route_sort(flat, self.num_experts)
+            ends = ends.to(torch.int64)
+            send_counts = (ends - torch.cat([ends.new_zeros(1), ends[:-1]])).reshape(W, EL)
+        else:
+            flat = topk_ids.reshape(-1).to(torch.int64)
+            send_perm = torch.argsort(flat, stable=True)
+            pair_to_sorted = torch.empty_like(send_perm)
+            pair_to_sorted[send_perm] = torch.arange(flat.numel(), device=device)
+            send_counts = torch.bincount(flat, minlength=self.num_experts).reshape(W, EL)
         if W > 1:
             recv_counts = torch.empty_like(send_counts)
             dist.all_to_all_single(recv_counts, send_counts, group=self.group)
@@ -83,10 +101,14 @@ class ExpertParallel:
         seg_of_row = torch.repeat_interleave(torch.arange(W * EL, device=device), cnt_em, output_size=rows_recv)
         within = torch.arange(rows_recv, device=device) - out_start[seg_of_row]
         recv_perm = seg_start_em[seg_of_row] + within
+        recv_inv = torch.empty_like(recv_perm)
+        recv_inv[recv_perm] = torch.arange(rows_recv, device=device)
+        if topk_ids.is_cuda:
+            recv_perm, recv_inv = recv_perm.to(torch.int32), recv_inv.to(torch.int32)
         expert_offsets = torch.cumsum(recv_counts.sum(0), 0).to(torch.int32)
         expert_indices = torch.arange(EL, device=device, dtype=torch.int64)
         return DispatchPlan(topk_ids.shape[1], send_perm, send_splits, recv_splits, recv_perm, expert_indices,
-                            expert_offsets, int(flat.numel()), rows_recv)
+                            expert_offsets, int(flat.numel()), rows_recv, pair_to_sorted, recv_inv)
 
     # ------------------------------------------------------------------ exchanges
     def _all_to_all(self, send: torch.Tensor, out_rows: int, out_splits, in_splits) -> torch.Tensor:
@@ -98,33 +120,54 @@ class ExpertParallel:
             recv.copy_(send)
         return recv
 
+    @staticmethod
+    def _gather(src: torch.Tensor, index: torch.Tensor, divisor: int = 1) -> torch.Tensor:
+        """out[r] = src[index[r] // divisor]; the CUDA kernel for bf16 rows, torch otherwise."""
+        if _native_rows(src) and index.dtype == torch.int32:
+            from . import native
+
+            return native.gather_rows(src, index, divisor)
+        idx = index.long()
+        if divisor != 1:
+            idx = torch.div(idx, divisor, rounding_mode="floor")
+        return src.index_select(0, idx)
+
     def dispatch_tokens(self, plan: DispatchPlan, x: torch.Tensor) -> torch.Tensor:
         """[tokens, width] -> [R_recv, width]: each token row replicated to its top_k experts,
         delivered to the owning ranks, expert-major."""
-        rows = x.index_select(0, torch.div(plan.send_perm, plan.top_k, rounding_mode="floor"))
-        return self.dispatch_rows_sorted(plan, rows)
+        return self.dispatch_rows_sorted(plan, self._gather(x, plan.send_perm, plan.top_k))
 
     def dispatch_rows(self, plan: DispatchPlan, rows: torch.Tensor) -> torch.Tensor:
         """[R_local, width] per routed row (token-major, slot-minor) -> [R_recv, width] expert-major."""
-        return self.dispatch_rows_sorted(plan, rows.index_select(0, plan.send_perm))
+        return self.dispatch_rows_sorted(plan, self._gather(rows, plan.send_perm))
 
     def dispatch_rows_sorted(self, plan: DispatchPlan, rows_sorted: torch.Tensor) -> torch.Tensor:
         recv = self._all_to_all(rows_sorted.contiguous(), plan.rows_recv, plan.recv_splits, plan.send_splits)
-        return recv.index_select(0, plan.recv_perm)
+        if self.world == 1:
+            return recv  # one rank: the sorted order already is expert-major
+        return self._gather(recv, plan.recv_perm)
+
+    def _return_sorted(self, plan: DispatchPlan, rows: torch.Tensor) -> torch.Tensor:
+        """[R_recv, width] expert-major -> [R_local, width] in this rank's send (sorted) order."""
+        if self.world == 1:
+            return rows
+        buf = self._gather(rows.contiguous(), plan.recv_inv)
+        return self._all_to_all(buf, plan.rows_local, plan.send_splits, plan.recv_splits)
 
     def combine_rows(self, plan: DispatchPlan, rows: torch.Tensor) -> torch.Tensor:
         """Inverse of ``dispatch_rows``: [R_recv, width] expert-major -> [R_local, width] per routed row."""
-        buf = torch.empty_like(rows)
-        buf.index_copy_(0, plan.recv_perm, rows)
-        back = self._all_to_all(buf, plan.rows_local, plan.send_splits, plan.recv_splits)
-        out = torch.empty_like(back)
-        out.index_copy_(0, plan.send_perm, back)
-        return out
+        return self._gather(self._return_sorted(plan, rows), plan.pair_to_sorted)
 
     def combine_tokens(self, plan: DispatchPlan, rows: torch.Tensor, weights: torch.Tensor | None = None):
         """``combine_rows`` followed by the sum over the top_k slots of every token (optionally
-        weighted by [tokens, top_k] routing weights), accumulated in fp32."""
-        per_row = self.combine_rows(plan, rows).reshape(-1, plan.top_k, rows.shape[1]).float()
+        weighted by [tokens, top_k] routing weights), accumulated in fp32 and rounded once."""
+        back = self._return_sorted(plan, rows)
+        if _native_rows(back) and plan.pair_to_sorted.dtype == torch.int32:
+            from . import native
+
+            w = None if weights is None else weights.reshape(-1).float().contiguous()
+            return native.combine_rows(back, plan.pair_to_sorted, plan.top_k, w)
+        per_row = back.index_select(0, plan.pair_to_sorted.long()).reshape(-1, plan.top_k, rows.shape[1]).float()
         if weights is not None:
             per_row = per_row * weights.reshape(-1, plan.top_k, 1).float()
         return per_row.sum(1).to(rows.dtype)
