@@ -143,6 +143,38 @@ int tgo_combine_rows(const void* rows, const int32_t* pair_to_sorted, const floa
 int tgo_quantize_q8(const void* x, int64_t rows, int64_t width, void* q, float* d, float* sum,
                     void* stream);
 
+/* ---- expert-parallel row exchange over peer memory (no counterpart in the reference, which is
+ * single-GPU).  One process per GPU; expert e lives on rank e / (num_experts / world).  Every rank
+ * owns a receive buffer of `capacity` rows that its peers can address (peer_ptrs[r] = rank r's
+ * buffer, e.g. from CUDA IPC / symmetric memory); rows are written into and read from those
+ * buffers with plain 16-byte peer stores and loads.  None of these calls waits for another GPU:
+ * the host layer orders the phases with stream-ordered collectives (dispatch | barrier | grouped
+ * matmul | barrier | pull). */
+
+/* From the per-expert pair counts of all ranks (counts_all int32[world][num_experts], identical
+ * on every rank) and this rank's routing (expert_ids, pair_to_sorted from tgo_route_sort):
+ * dst_rank / dst_row int32[n_pairs] = where each routed pair goes (-1 if dropped; *overflow is set
+ * to 1 if a row would not fit in `capacity`), and the group metadata of the local experts in the
+ * receive buffer (local_indices int64[E/world], local_offsets int32[E/world]: the contract of
+ * validate_grouped_mmq, csrc/mmq_hip.cu:325-406).  scratch: int32[2 * num_experts]. */
+int tgo_ep_plan(const int32_t* counts_all, int64_t world, int64_t num_experts, int64_t my_rank,
+                const int32_t* expert_ids, const int32_t* pair_to_sorted, int64_t n_pairs,
+                int64_t capacity, int32_t* dst_rank, int32_t* dst_row, int64_t* local_indices,
+                int32_t* local_offsets, int32_t* scratch, int32_t* overflow, void* stream);
+
+/* peer[dst_rank[i]][dst_row[i]][:] = src[i / divisor][:] for bf16 rows of `width` (multiple of 8).
+ * peer_ptrs is a HOST array of `world` device pointers. */
+int tgo_ep_dispatch(const void* src, int64_t divisor, const int32_t* dst_rank, const int32_t* dst_row,
+                    int64_t n_pairs, int64_t width, void* const* peer_ptrs, int64_t world,
+                    void* stream);
+
+/* out[t][:] = sum over the `group` consecutive pairs of t of weights[pair] * peer[dst_rank][dst_row][:]
+ * (group = 1: one row per pair; group = top_k: the per-token combine; fp32 accumulation, one bf16
+ * rounding; weights may be null = 1). */
+int tgo_ep_pull(void* const* peer_ptrs, int64_t world, const int32_t* dst_rank, const int32_t* dst_row,
+                const float* weights, void* out, int64_t n_out, int64_t group, int64_t width,
+                void* stream);
+
 /* Grouped forward for callers that cannot hand over a workspace and must not trigger a device
  * allocation: the same operation and results as tgo_grouped_fwd, with the tile list kept in a
  * fixed array inside the library instead of caller memory.  No counterpart in the reference.

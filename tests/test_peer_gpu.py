@@ -1,0 +1,112 @@
+"""GPU tests of the peer-memory expert-parallel exchange.  Several virtual ranks are emulated on
+one GPU (their receive buffers are ordinary allocations on the same device and every phase is a
+separate stream-ordered launch, so nothing ever waits on another kernel): plan, dispatch, grouped
+matmul and pull are checked against the host oracle.  A real multi-GPU run is the benchmark's job."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import blocks, ref
+from helpers import DX_TOL, FWD_TOL, bits, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_virtual_ranks_dispatch_matmul_pull(cuda, world):
+    from torch_ggml_ops_b200 import native
+
+    qt, E, N, K, tokens, top_k, cap = ref.Q4_K, 16, 64, 256, 150, 4, 1024
+    EL = E // world
+    w = blocks.expert_weights(qt, E, N, K, 3)
+    W = torch.from_numpy(ref.expert_weights_fp32(w, qt, N, K))
+    ids = [blocks.topk_routing(tokens, E, top_k, seed=10 + r) for r in range(world)]
+    xs = [blocks.gaussian_bf16((tokens, K), 20 + r) for r in range(world)]
+    dys = [blocks.gaussian_bf16((tokens * top_k, N), 30 + r) for r in range(world)]
+    flat = [to_dev(i.reshape(-1).astype(np.int32)) for i in ids]
+    sorts = [native.route_sort(f, E) for f in flat]
+    counts_all = torch.stack([torch.diff(s[3], prepend=s[3].new_zeros(1)) for s in sorts]).contiguous()
+    plans = [native.ep_plan(counts_all, r, flat[r], sorts[r][1], cap) for r in range(world)]
+    assert all(int(p[4].item()) == 0 for p in plans)
+    x_in = [torch.full((cap, K), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    y_out = [torch.full((cap, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    dy_in = [torch.zeros((cap, N), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    dx_out = [torch.zeros((cap, K), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    ptrs = lambda bufs: [b.data_ptr() for b in bufs]  # noqa: E731
+    for r in range(world):
+        native.ep_dispatch(to_dev(xs[r]), top_k, plans[r][0], plans[r][1], ptrs(x_in))
+        native.ep_dispatch(to_dev(dys[r]), 1, plans[r][0], plans[r][1], ptrs(dy_in))
+    torch.cuda.synchronize()
+    # layout of every owner's buffer: (local expert, source rank, order of the source's stable sort)
+    for o in range(world):
+        want_rows = []
+        for le in range(EL):
+            e = o * EL + le
+            for s in range(world):
+                f = ids[s].reshape(-1)
+                for i in np.nonzero(f == e)[0]:
+                    want_rows.append(xs[s][i // top_k])
+        want = torch.stack(want_rows) if want_rows else torch.empty(0, K, dtype=torch.bfloat16)
+        assert np.array_equal(bits(x_in[o][: len(want_rows)]), bits(want))
+        offs = plans[o][3].cpu().numpy()
+        assert offs[-1] == len(want_rows)
+        assert plans[o][2].tolist() == list(range(EL))
+    # owners run the grouped operators over their whole buffer; group offsets say which rows exist
+    wdev = to_dev(w)
+    for o in range(world):
+        ws = torch.empty(native.grouped_workspace_bytes(cap, EL), dtype=torch.uint8, device="cuda")
+        wl = wdev[o * EL:(o + 1) * EL].contiguous()
+        native.grouped_fwd(x_in[o], wl, None, y_out[o], None, plans[o][2], plans[o][3], EL, cap, N, K, qt, ws)
+        native.grouped_dx(dy_in[o], None, wl, None, dx_out[o], plans[o][2], plans[o][3], EL, cap, N, K, qt, ws)
+    gate = torch.rand(tokens, top_k)
+    for r in range(world):
+        y = torch.empty(tokens * top_k, N, dtype=torch.bfloat16, device="cuda")
+        native.ep_pull(ptrs(y_out), plans[r][0], plans[r][1], y, 1)
+        dx = torch.empty(tokens, K, dtype=torch.bfloat16, device="cuda")
+        native.ep_pull(ptrs(dx_out), plans[r][0], plans[r][1], dx, top_k, to_dev(gate.reshape(-1).contiguous()))
+        f = ids[r].reshape(-1)
+        xf = xs[r].float()
+        want_y = torch.stack([xf[i // top_k] @ W[f[i]].t() for i in range(f.size)])
+        want_dx = torch.zeros(tokens, K)
+        for i in range(f.size):
+            want_dx[i // top_k] += gate.reshape(-1)[i] * (dys[r][i].float() @ W[f[i]])
+        assert ref.rel_frobenius(y.float().cpu(), want_y) < FWD_TOL
+        assert ref.rel_frobenius(dx.float().cpu(), want_dx) < DX_TOL
+    assert native.device_status() == 0
+
+
+def test_capacity_overflow_is_flagged_not_written(cuda):
+    from torch_ggml_ops_b200 import native
+
+    E, tokens, top_k, cap = 4, 64, 2, 16
+    ids = blocks.topk_routing(tokens, E, top_k, seed=1)
+    flat = to_dev(ids.reshape(-1).astype(np.int32))
+    _, p2s, _, ends = native.route_sort(flat, E)
+    counts = torch.diff(ends, prepend=ends.new_zeros(1)).reshape(1, E).contiguous()
+    dst_rank, dst_row, _, _, overflow = native.ep_plan(counts, 0, flat, p2s, cap)
+    assert int(overflow.item()) == 1
+    kept = dst_rank.cpu().numpy() >= 0
+    assert kept.sum() == cap and int(dst_row.max().item()) == cap - 1
+
+
+def test_single_rank_wrapper(cuda):
+    from torch_ggml_ops_b200.peer_parallel import PeerExpertParallel
+
+    qt, E, N, K, tokens, top_k = ref.Q5_K, 8, 128, 512, 100, 2
+    w = blocks.expert_weights(qt, E, N, K, 4)
+    W = torch.from_numpy(ref.expert_weights_fp32(w, qt, N, K))
+    ids = blocks.topk_routing(tokens, E, top_k, seed=2)
+    x = blocks.gaussian_bf16((tokens, K), 5)
+    dy = blocks.gaussian_bf16((tokens * top_k, N), 6)
+    pep = PeerExpertParallel(to_dev(w), qt, E, N, K, capacity_rows=512)
+    plan = pep.plan(to_dev(torch.from_numpy(ids)))
+    y = pep.forward(plan, to_dev(x))
+    dx = pep.grad_input(plan, to_dev(dy))
+    f = ids.reshape(-1)
+    want_y = torch.stack([x[i // top_k].float() @ W[f[i]].t() for i in range(f.size)])
+    want_dx = torch.zeros(tokens, K)
+    for i in range(f.size):
+        want_dx[i // top_k] += dy[i].float() @ W[f[i]]
+    assert ref.rel_frobenius(y.float().cpu(), want_y) < FWD_TOL
+    assert ref.rel_frobenius(dx.float().cpu(), want_dx) < DX_TOL
+    assert int(pep.overflow.item()) == 0

@@ -1,0 +1,211 @@
+// Expert-parallel row exchange over peer memory (NVLink / NVSwitch): routed rows are written
+// straight into the expert-major receive buffer of the GPU that owns their expert, and results are
+// read back from the owner's buffer, each in ONE pass of plain 16-byte peer stores / loads.  No
+// multicast, no waits inside these kernels: ranks are ordered by stream-ordered collectives issued
+// by the host layer between the phases.
+//
+// The reference is single-GPU; its contract "rows sorted by expert + cumulative end offsets"
+// (csrc/mmq_hip.cu:325-406) is what tgo_ep_plan produces for the local experts of every rank.
+#include "../../include/tgo_mmq.h"
+
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace tgo {
+
+int route_fail(int code, const char* msg);  // tgo_api.cu
+
+constexpr int kEpMaxRanks = 64;
+
+// counts[s][e]: routed pairs of rank s for (global) expert e.  Expert e lives on rank e / EL, in
+// whose buffer rows are ordered by (local expert, source rank, position in the source's sorted
+// order).  One block.
+__global__ void __launch_bounds__(1024) ep_offsets_kernel(const int32_t* __restrict__ counts, int W, int E, int EL, int me,
+                                                          int32_t* __restrict__ dst_base, int32_t* __restrict__ seg_start,
+                                                          int64_t* __restrict__ local_indices,
+                                                          int32_t* __restrict__ local_offsets) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int first = (e / EL) * EL;
+        int before_experts = 0;   // rows of earlier experts of the same owner, all sources
+        for (int f = first; f < e; ++f)
+            for (int s = 0; s < W; ++s) before_experts += counts[s * E + f];
+        int before_sources = 0, total = 0;
+        for (int s = 0; s < W; ++s) {
+            const int c = counts[s * E + e];
+            if (s < me) before_sources += c;
+            total += c;
+        }
+        dst_base[e] = before_experts + before_sources;
+        int mine_before = 0;
+        for (int f = 0; f < e; ++f) mine_before += counts[me * E + f];
+        seg_start[e] = mine_before;
+        if (e / EL == me) {
+            local_indices[e - first] = e - first;
+            local_offsets[e - first] = before_experts + total;
+        }
+    }
+}
+
+// Destination (rank, row) of every routed pair of this rank.
+__global__ void __launch_bounds__(256) ep_map_kernel(const int32_t* __restrict__ expert_ids, const int32_t* __restrict__ pair_to_sorted,
+                                                     const int32_t* __restrict__ dst_base, const int32_t* __restrict__ seg_start,
+                                                     int n_pairs, int E, int EL, int capacity, int32_t* __restrict__ dst_rank,
+                                                     int32_t* __restrict__ dst_row, int* __restrict__ overflow) {
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= n_pairs) return;
+    const int e = expert_ids[i];
+    const int j = pair_to_sorted[i];
+    if (e < 0 || e >= E || j < 0) {
+        dst_rank[i] = -1;
+        dst_row[i] = -1;
+        return;
+    }
+    const int row = dst_base[e] + (j - seg_start[e]);
+    if (row >= capacity) {  // receive buffer too small: drop the pair and say so
+        dst_rank[i] = -1;
+        dst_row[i] = -1;
+        atomicExch(overflow, 1);
+        return;
+    }
+    dst_rank[i] = e / EL;
+    dst_row[i] = row;
+}
+
+struct PeerPtrs {
+    void* p[kEpMaxRanks];
+};
+
+// peer[dst_rank[i]][dst_row[i]][:] = src[i / divisor][:]   (rows of vec_per_row 16-byte vectors)
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restrict__ src, int divisor, const int32_t* __restrict__ dst_rank,
+                                                          const int32_t* __restrict__ dst_row, long long n_pairs, int vec_per_row,
+                                                          const __grid_constant__ PeerPtrs peers) {
+    const long long total = n_pairs * vec_per_row;
+    for (long long v = blockIdx.x * 256LL + threadIdx.x; v < total; v += 256LL * gridDim.x) {
+        const long long i = v / vec_per_row;
+        const int c = static_cast<int>(v - i * vec_per_row);
+        const int r = dst_rank[i];
+        if (r < 0) continue;
+        const uint4 val = src[(i / divisor) * vec_per_row + c];
+        static_cast<uint4*>(peers.p[r])[static_cast<long long>(dst_row[i]) * vec_per_row + c] = val;
+    }
+}
+
+// out[t][:] = sum over the `group` consecutive pairs of t of weight * peer[dst_rank][dst_row][:]
+// (group = 1: one output row per pair; group = top_k: the per-token combine), fp32 accumulation.
+__global__ void __launch_bounds__(256) ep_pull_kernel(const __grid_constant__ PeerPtrs peers, const int32_t* __restrict__ dst_rank,
+                                                      const int32_t* __restrict__ dst_row, const float* __restrict__ weights,
+                                                      uint4* __restrict__ out, long long n_out, int group, int vec_per_row) {
+    const long long total = n_out * vec_per_row;
+    for (long long v = blockIdx.x * 256LL + threadIdx.x; v < total; v += 256LL * gridDim.x) {
+        const long long t = v / vec_per_row;
+        const int c = static_cast<int>(v - t * vec_per_row);
+        if (group == 1) {
+            const int r = dst_rank[t];
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (r >= 0) val = static_cast<const uint4*>(peers.p[r])[static_cast<long long>(dst_row[t]) * vec_per_row + c];
+            out[v] = val;
+            continue;
+        }
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < group; ++s) {
+            const long long i = t * group + s;
+            const int r = dst_rank[i];
+            if (r < 0) continue;
+            const float w = weights != nullptr ? weights[i] : 1.0f;
+            const uint4 val = static_cast<const uint4*>(peers.p[r])[static_cast<long long>(dst_row[i]) * vec_per_row + c];
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&val);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h[j]);
+                acc[2 * j] = fmaf(w, f.x, acc[2 * j]);
+                acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]);
+            }
+        }
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        out[v] = o;
+    }
+}
+
+static int ep_grid(long long work_items) {
+    long long blocks = (work_items + 255) / 256;
+    if (blocks > 148LL * 8) blocks = 148LL * 8;
+    return static_cast<int>(blocks < 1 ? 1 : blocks);
+}
+
+static int ep_launch_check(const char* what) {
+    return cudaGetLastError() == cudaSuccess ? TGO_OK : route_fail(TGO_E_CUDA, what);
+}
+
+static int fill_peers(PeerPtrs& pp, void* const* peer_ptrs, int64_t world) {
+    if (peer_ptrs == nullptr || world <= 0 || world > kEpMaxRanks) return route_fail(TGO_E_ARG, "world size must be in 1..64");
+    for (int r = 0; r < world; ++r) {
+        if (peer_ptrs[r] == nullptr || (reinterpret_cast<uintptr_t>(peer_ptrs[r]) & 15u) != 0)
+            return route_fail(TGO_E_ARG, "peer buffers must be non-null and 16-byte aligned");
+        pp.p[r] = peer_ptrs[r];
+    }
+    return TGO_OK;
+}
+
+}  // namespace tgo
+
+using namespace tgo;
+
+extern "C" {
+
+int tgo_ep_plan(const int32_t* counts_all, int64_t world, int64_t num_experts, int64_t my_rank, const int32_t* expert_ids,
+                const int32_t* pair_to_sorted, int64_t n_pairs, int64_t capacity, int32_t* dst_rank, int32_t* dst_row,
+                int64_t* local_indices, int32_t* local_offsets, int32_t* scratch, int32_t* overflow, void* stream) {
+    if (counts_all == nullptr || expert_ids == nullptr || pair_to_sorted == nullptr || dst_rank == nullptr ||
+        dst_row == nullptr || local_indices == nullptr || local_offsets == nullptr || scratch == nullptr || overflow == nullptr)
+        return route_fail(TGO_E_ARG, "null pointer");
+    if (world <= 0 || world > kEpMaxRanks || my_rank < 0 || my_rank >= world)
+        return route_fail(TGO_E_ARG, "world size must be in 1..64 and the rank inside it");
+    if (num_experts <= 0 || num_experts > 4096 || num_experts % world != 0)
+        return route_fail(TGO_E_ARG, "num_experts must be in 1..4096 and divisible by the world size");
+    if (n_pairs <= 0 || n_pairs > INT32_MAX || capacity <= 0 || capacity > INT32_MAX)
+        return route_fail(TGO_E_ARG, "n_pairs and capacity must be in 1..2^31-1");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int E = static_cast<int>(num_experts), W = static_cast<int>(world), EL = E / W;
+    ep_offsets_kernel<<<1, 1024, 0, s>>>(counts_all, W, E, EL, static_cast<int>(my_rank), scratch, scratch + E,
+                                         local_indices, local_offsets);
+    ep_map_kernel<<<static_cast<int>((n_pairs + 255) / 256), 256, 0, s>>>(
+        expert_ids, pair_to_sorted, scratch, scratch + E, static_cast<int>(n_pairs), E, EL, static_cast<int>(capacity),
+        dst_rank, dst_row, overflow);
+    return ep_launch_check("expert-parallel plan kernel launch failed");
+}
+
+int tgo_ep_dispatch(const void* src, int64_t divisor, const int32_t* dst_rank, const int32_t* dst_row, int64_t n_pairs,
+                    int64_t width, void* const* peer_ptrs, int64_t world, void* stream) {
+    if (src == nullptr || dst_rank == nullptr || dst_row == nullptr) return route_fail(TGO_E_ARG, "null pointer");
+    if (n_pairs <= 0 || width <= 0 || (width * 2) % 16 != 0 || divisor <= 0 || divisor > INT32_MAX)
+        return route_fail(TGO_E_ARG, "dispatch needs pairs > 0, a row length that is a multiple of 8 and divisor > 0");
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) != 0) return route_fail(TGO_E_ARG, "src must be 16-byte aligned");
+    PeerPtrs pp = {};
+    const int rc = fill_peers(pp, peer_ptrs, world);
+    if (rc != TGO_OK) return rc;
+    const int vec = static_cast<int>(width / 8);
+    ep_dispatch_kernel<<<ep_grid(n_pairs * vec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(src), static_cast<int>(divisor), dst_rank, dst_row, n_pairs, vec, pp);
+    return ep_launch_check("ep_dispatch_kernel launch failed");
+}
+
+int tgo_ep_pull(void* const* peer_ptrs, int64_t world, const int32_t* dst_rank, const int32_t* dst_row, const float* weights,
+                void* out, int64_t n_out, int64_t group, int64_t width, void* stream) {
+    if (dst_rank == nullptr || dst_row == nullptr || out == nullptr) return route_fail(TGO_E_ARG, "null pointer");
+    if (n_out <= 0 || group <= 0 || group > 1024 || width <= 0 || (width * 2) % 16 != 0)
+        return route_fail(TGO_E_ARG, "pull needs rows > 0, 1 <= group <= 1024 and a row length that is a multiple of 8");
+    if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return route_fail(TGO_E_ARG, "out must be 16-byte aligned");
+    PeerPtrs pp = {};
+    const int rc = fill_peers(pp, peer_ptrs, world);
+    if (rc != TGO_OK) return rc;
+    const int vec = static_cast<int>(width / 8);
+    ep_pull_kernel<<<ep_grid(n_out * vec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        pp, dst_rank, dst_row, weights, static_cast<uint4*>(out), n_out, static_cast<int>(group), vec);
+    return ep_launch_check("ep_pull_kernel launch failed");
+}
+
+}  // extern "C"

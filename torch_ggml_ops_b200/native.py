@@ -33,6 +33,9 @@ SIGNATURES = {
     "tgo_gather_rows": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _vp]),
     "tgo_combine_rows": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tgo_quantize_q8": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "tgo_ep_plan": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "tgo_ep_dispatch": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "tgo_ep_pull": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tgo_grouped_fwd_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
 }
 
@@ -187,3 +190,37 @@ def quantize_q8(x, stream=None):
     s = torch.empty((rows, width // 32), dtype=torch.float32, device=x.device)
     check(lib().tgo_quantize_q8(_ptr(x), rows, width, _ptr(q), _ptr(d), _ptr(s), _stream(stream)), "tgo_quantize_q8")
     return q, d, s
+
+
+def _ptr_array(ptrs):
+    return (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+
+
+def ep_plan(counts_all, my_rank, expert_ids, pair_to_sorted, capacity, stream=None):
+    """Destination of every routed pair and the local group metadata; see ``tgo_ep_plan``.
+    ``counts_all``: int32 [world, E] on the GPU.  Returns (dst_rank, dst_row, local_indices,
+    local_offsets, overflow_flag)."""
+    import torch
+
+    world, E = counts_all.shape
+    n, dev = expert_ids.numel(), expert_ids.device
+    dst_rank = torch.empty(n, dtype=torch.int32, device=dev)
+    dst_row = torch.empty(n, dtype=torch.int32, device=dev)
+    li = torch.empty(E // world, dtype=torch.int64, device=dev)
+    lo = torch.empty(E // world, dtype=torch.int32, device=dev)
+    scratch = torch.empty(2 * E, dtype=torch.int32, device=dev)
+    overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+    check(lib().tgo_ep_plan(_ptr(counts_all), world, E, my_rank, _ptr(expert_ids), _ptr(pair_to_sorted), n, capacity,
+                            _ptr(dst_rank), _ptr(dst_row), _ptr(li), _ptr(lo), _ptr(scratch), _ptr(overflow),
+                            _stream(stream)), "tgo_ep_plan")
+    return dst_rank, dst_row, li, lo, overflow
+
+
+def ep_dispatch(src, divisor, dst_rank, dst_row, peer_ptrs, stream=None) -> None:
+    check(lib().tgo_ep_dispatch(_ptr(src), divisor, _ptr(dst_rank), _ptr(dst_row), dst_rank.numel(), src.shape[1],
+                                _ptr_array(peer_ptrs), len(peer_ptrs), _stream(stream)), "tgo_ep_dispatch")
+
+
+def ep_pull(peer_ptrs, dst_rank, dst_row, out, group=1, weights=None, stream=None) -> None:
+    check(lib().tgo_ep_pull(_ptr_array(peer_ptrs), len(peer_ptrs), _ptr(dst_rank), _ptr(dst_row), _ptr(weights),
+                            _ptr(out), out.shape[0], group, out.shape[1], _stream(stream)), "tgo_ep_pull")

@@ -1,0 +1,122 @@
+"""Expert-parallel grouped matmul with the row exchange done by this library's own kernels over
+peer memory (NVLink / NVSwitch) instead of NCCL all-to-alls.
+
+One process per GPU.  Every rank owns four receive / result buffers that its peers can address
+(torch symmetric memory; plain tensors on one rank).  A step is
+
+    route_sort -> all_gather(counts) -> tgo_ep_plan             (where does every routed pair go)
+    tgo_ep_dispatch(x)   | fence | grouped forward  | fence | tgo_ep_pull(y)
+    tgo_ep_dispatch(dy)  | fence | grouped dX       | fence | tgo_ep_pull(dx, summed over top-k)
+
+Rows cross NVLink exactly once per exchange, written (dispatch) or read (pull) by plain 16-byte
+peer stores / loads straight into / out of the expert-major layout the grouped kernels consume, so
+there is no permutation pass on either side and no host read of the routing: the grouped kernels
+are launched over the whole receive buffer (`capacity` rows) and the device-side group offsets say
+which rows exist.  "fence" is a stream-ordered one-element all-reduce: it orders the ranks'
+phases without any spin-wait in our kernels.  Multicast is never used (the symmetric-memory
+allocator is told not to bind a multicast object).
+
+The reference has no multi-GPU path; the per-rank contract it defines (rows sorted by expert +
+int64 expert ids + int32 cumulative end offsets, csrc/mmq_hip.cu:325-406) is what each rank's
+buffers satisfy.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import native
+
+
+class PeerExpertParallel:
+    """Fused dispatch / grouped matmul / combine for one MoE projection [E, N, K] of quant type
+    ``quant_type``; ``local_weight`` is this rank's shard [E / world, N, row_bytes] (uint8, CUDA)."""
+
+    def __init__(self, local_weight: torch.Tensor, quant_type: int, num_experts: int, out_features: int,
+                 in_features: int, capacity_rows: int, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if num_experts % self.world:
+            raise ValueError(f"{num_experts} experts do not divide over {self.world} ranks")
+        if local_weight.shape[0] != num_experts // self.world:
+            raise ValueError("local_weight must hold this rank's num_experts / world experts")
+        self.weight, self.qt = local_weight, int(quant_type)
+        self.E, self.EL = num_experts, num_experts // self.world
+        self.N, self.K, self.cap = int(out_features), int(in_features), int(capacity_rows)
+        dev = local_weight.device
+        self.device = dev
+        shapes = {"x_in": self.K, "y_out": self.N, "dy_in": self.N, "dx_out": self.K}
+        self.buf, self.peers = {}, {}
+        if self.world > 1:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+
+            for name, width in shapes.items():
+                t = symm_mem.empty(self.cap, width, dtype=torch.bfloat16, device=dev)
+                hdl = symm_mem.rendezvous(t, dist.group.WORLD if group is None else group)
+                self.buf[name] = t
+                self.peers[name] = [int(p) for p in hdl.buffer_ptrs]
+                self.buf[name + "_hdl"] = hdl  # keeps the mapping alive
+        else:
+            for name, width in shapes.items():
+                t = torch.empty(self.cap, width, dtype=torch.bfloat16, device=dev)
+                self.buf[name] = t
+                self.peers[name] = [t.data_ptr()]
+        self.ws = torch.empty(native.grouped_workspace_bytes(self.cap, self.EL), dtype=torch.uint8, device=dev)
+        self._token = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.overflow = None
+
+    # ------------------------------------------------------------------ ordering between ranks
+    def _fence(self) -> None:
+        """All ranks have finished everything they enqueued before this point (stream-ordered)."""
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.group)
+
+    # ------------------------------------------------------------------ routing
+    def plan(self, topk_ids: torch.Tensor):
+        """``topk_ids``: integer [tokens, top_k] global expert ids on this rank's GPU."""
+        flat = topk_ids.reshape(-1).to(torch.int32)
+        _, p2s, _, ends = native.route_sort(flat, self.E)
+        counts = torch.diff(ends, prepend=ends.new_zeros(1))
+        if self.world > 1:
+            counts_all = torch.empty(self.world, self.E, dtype=torch.int32, device=self.device)
+            dist.all_gather_into_tensor(counts_all, counts, group=self.group)
+        else:
+            counts_all = counts.reshape(1, self.E)
+        dst_rank, dst_row, li, lo, overflow = native.ep_plan(counts_all.contiguous(), self.rank, flat, p2s, self.cap)
+        self.overflow = overflow  # device flag: a row did not fit in `capacity_rows` (read it when convenient)
+        return {"top_k": topk_ids.shape[1], "dst_rank": dst_rank, "dst_row": dst_row, "indices": li, "offsets": lo}
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, plan, x_tokens: torch.Tensor) -> torch.Tensor:
+        """[tokens, K] bf16 -> [tokens * top_k, N]: every routed pair's expert projection."""
+        k = plan["top_k"]
+        native.ep_dispatch(x_tokens, k, plan["dst_rank"], plan["dst_row"], self.peers["x_in"])
+        self._fence()
+        native.grouped_fwd(self.buf["x_in"], self.weight, None, self.buf["y_out"], None, plan["indices"],
+                           plan["offsets"], self.EL, self.cap, self.N, self.K, self.qt, self.ws)
+        self._fence()
+        y = torch.empty(x_tokens.shape[0] * k, self.N, dtype=torch.bfloat16, device=self.device)
+        native.ep_pull(self.peers["y_out"], plan["dst_rank"], plan["dst_row"], y, 1)
+        return y
+
+    # ------------------------------------------------------------------ input gradient
+    def grad_input(self, plan, dy_pairs: torch.Tensor, weights: torch.Tensor | None = None) -> torch.Tensor:
+        """[tokens * top_k, N] cotangents per routed pair -> [tokens, K]: dX summed over the top-k
+        slots of each token (optionally weighted), fp32 accumulation, one bf16 rounding."""
+        k = plan["top_k"]
+        native.ep_dispatch(dy_pairs, 1, plan["dst_rank"], plan["dst_row"], self.peers["dy_in"])
+        self._fence()
+        native.grouped_dx(self.buf["dy_in"], None, self.weight, None, self.buf["dx_out"], plan["indices"],
+                          plan["offsets"], self.EL, self.cap, self.N, self.K, self.qt, self.ws)
+        self._fence()
+        dx = torch.empty(dy_pairs.shape[0] // k, self.K, dtype=torch.bfloat16, device=self.device)
+        w = None if weights is None else weights.reshape(-1).float().contiguous()
+        native.ep_pull(self.peers["dx_out"], plan["dst_rank"], plan["dst_row"], dx, k, w)
+        return dx
+
+
+__all__ = ["PeerExpertParallel"]
