@@ -271,26 +271,51 @@ def gpu_arm(args):
         dyh = dy_sorted.cpu().pin_memory()
         yh = torch.empty(R, N, dtype=torch.bfloat16).pin_memory()
         dxh = torch.empty(R, K, dtype=torch.bfloat16).pin_memory()
-        xd = torch.empty(R, K, dtype=torch.bfloat16, device=dev, requires_grad=True)
-        dyd = torch.empty(R, N, dtype=torch.bfloat16, device=dev)
+        # Three streams, two sets of device buffers: the host->device copy of step i+1 and the
+        # device->host copy of step i-1 overlap the matmuls of step i (PCIe is full duplex).  Every
+        # step still copies all of its inputs in and all of its results out inside the timed region.
+        s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        xd = [torch.empty(R, K, dtype=torch.bfloat16, device=dev, requires_grad=True) for _ in range(2)]
+        dyd = [torch.empty(R, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_cmp = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
 
-        def step_e2e():
-            with torch.no_grad():
-                xd.copy_(xh, non_blocking=True)
-                dyd.copy_(dyh, non_blocking=True)
-            xd.grad = None
-            out = tgo.grouped_mmq(xd, w, ei, eo, qt, N)
-            out.backward(dyd)
-            yh.copy_(out.detach(), non_blocking=True)
-            dxh.copy_(xd.grad, non_blocking=True)
+        def step_e2e(i):
+            b = i & 1
+            with torch.cuda.stream(s_in), torch.no_grad():
+                s_in.wait_event(ev_cmp[b])          # the matmuls that last read these buffers are done
+                xd[b].copy_(xh, non_blocking=True)
+                dyd[b].copy_(dyh, non_blocking=True)
+                ev_in[b].record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_in[b])
+                xd[b].grad = None
+                out = tgo.grouped_mmq(xd[b], w, ei, eo, qt, N)
+                out.backward(dyd[b])
+                ev_cmp[b].record(s_cmp)
+                grad = xd[b].grad
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cmp[b])
+                out.record_stream(s_out)
+                grad.record_stream(s_out)
+                yh.copy_(out.detach(), non_blocking=True)
+                dxh.copy_(grad, non_blocking=True)
+                ev_out[b].record(s_out)
 
-        for _ in range(3):
-            step_e2e()
+        def run_e2e(n):
+            for st in (s_in, s_cmp, s_out):
+                st.wait_stream(torch.cuda.current_stream())
+            for i in range(n):
+                step_e2e(i)
+            for st in (s_in, s_cmp, s_out):
+                torch.cuda.current_stream().wait_stream(st)
+
+        run_e2e(3)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(args.steps):
-            step_e2e()
+        run_e2e(args.steps)
         e1.record()
         barrier()
         e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
@@ -320,8 +345,20 @@ def gpu_arm(args):
     else:
         # ---------------------------------------------------------------- expert parallel
         w_local = w  # already the local shard [EL, N, row_bytes]
+        pep = None
+        if args.exchange == "peer":
+            from torch_ggml_ops_b200.peer_parallel import PeerExpertParallel
 
-        def step_ep():
+            # receive buffers sized for twice the mean load of a rank (the routing is skewed)
+            pep = PeerExpertParallel(w_local, qt, E, N, K, capacity_rows=2 * R)
+
+        def step_peer():
+            plan = pep.plan(ids)
+            y_back = pep.forward(plan, x_tok)
+            dx_back = pep.grad_input(plan, dy_rows)
+            return y_back, dx_back
+
+        def step_nccl():
             plan = ep.plan(ids)
             rows = ep.dispatch_tokens(plan, x_tok).requires_grad_(True)
             out = tgo.grouped_mmq(rows, w_local, plan.expert_indices, plan.expert_offsets, qt, N)
@@ -330,6 +367,8 @@ def gpu_arm(args):
             out.backward(dy_here)
             dx_back = ep.combine_tokens(plan, rows.grad)                 # dX summed over the top-k slots
             return y_back, dx_back
+
+        step_ep = step_peer if pep is not None else step_nccl
 
         for _ in range(max(args.warmup, 3)):
             step_ep()
@@ -369,9 +408,13 @@ def gpu_arm(args):
         e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
         h2d = xh.numel() * 2 + dyh.numel() * 2
         d2h = yh.numel() * 2 + dxh.numel() * 2
-        launches = 4
+        launches = 4 + (3 + 2 + 4 if pep is not None else 3 + 6)  # GEMMs + tile builders, routing sort, plan, exchange kernels
         result["device_status"] = native.device_status()
-        parallelism = f"ep{world} (experts sharded, NCCL all-to-all dispatch/combine)"
+        if pep is not None:
+            result["ep_overflow"] = int(pep.overflow.item())
+            parallelism = f"ep{world} (experts sharded; dispatch/combine by peer-memory kernels over NVLink, NCCL only for counts and fences)"
+        else:
+            parallelism = f"ep{world} (experts sharded, NCCL all-to-all dispatch/combine)"
 
     if rank == 0:
         value = flops_step / (ms_step * 1e-3) / 1e12
@@ -427,6 +470,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="multi-GPU row exchange: this library's peer-memory kernels, or NCCL all-to-all")
     ap.add_argument("--profile", action="store_true",
                     help="single GPU only: run warm-up + steps of the device-resident step and exit (for ncu)")
     args = ap.parse_args()
