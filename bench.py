@@ -128,11 +128,22 @@ class ClockSampler:
 
 
 def keep_busy_for(seconds, fn):
-    """Repeat fn for at least `seconds` so the clock sampler sees the GPU under this load."""
+    """Repeat fn for about `seconds` so the clock sampler sees the GPU under this load.  The number
+    of repetitions is agreed between the ranks first: fn may contain collectives, and ranks that
+    each watched their own clock would leave the loop after different counts and deadlock."""
+    import torch.distributed as dist
+
+    fn()
+    torch.cuda.synchronize()
     t0 = time.time()
-    while time.time() - t0 < seconds:
+    fn()
+    torch.cuda.synchronize()
+    n = torch.tensor([max(1, min(20000, int(seconds / max(time.time() - t0, 1e-5))))], device="cuda", dtype=torch.int64)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(n, op=dist.ReduceOp.MAX)
+    for _ in range(int(n.item())):
         fn()
-        torch.cuda.synchronize()
+    torch.cuda.synchronize()
 
 
 # ------------------------------------------------------------------------------ CPU arm
@@ -349,14 +360,42 @@ def gpu_arm(args):
         if args.exchange == "peer":
             from torch_ggml_ops_b200.peer_parallel import PeerExpertParallel
 
-            # receive buffers sized for twice the mean load of a rank (the routing is skewed)
-            pep = PeerExpertParallel(w_local, qt, E, N, K, capacity_rows=2 * R)
+            # The tokens of a rank are processed as `--micro` micro-batches, each with its own
+            # receive buffers and stream, so the NVLink exchange of one overlaps the matmuls of the
+            # other.  Receive buffers are sized for twice the mean load (the routing is skewed).
+            nmb = max(1, args.micro)
+            mb_tok = T // nmb
+            peps = [PeerExpertParallel(w_local, qt, E, N, K, capacity_rows=2 * mb_tok * top_k) for _ in range(nmb)]
+            pep = peps[0]
+            mb_streams = [torch.cuda.Stream() for _ in range(nmb)]
+            ids32 = ids.to(torch.int32)
+            mb_ids = [ids32[i * mb_tok:(i + 1) * mb_tok].contiguous() for i in range(nmb)]
+            mb_x = [x_tok[i * mb_tok:(i + 1) * mb_tok] for i in range(nmb)]
+            mb_dy = [dy_rows[i * mb_tok * top_k:(i + 1) * mb_tok * top_k] for i in range(nmb)]
+            y_all = torch.empty(R, N, dtype=torch.bfloat16, device=dev)
+            dx_all = torch.empty(T, K, dtype=torch.bfloat16, device=dev)
+            mb_y = [y_all[i * mb_tok * top_k:(i + 1) * mb_tok * top_k] for i in range(nmb)]
+            mb_dx = [dx_all[i * mb_tok:(i + 1) * mb_tok] for i in range(nmb)]
 
         def step_peer():
-            plan = pep.plan(ids)
-            y_back = pep.forward(plan, x_tok)
-            dx_back = pep.grad_input(plan, dy_rows)
-            return y_back, dx_back
+            # phases are issued round-robin over the micro-batches so that every rank enqueues its
+            # collectives (counts all-gather, fences) in the same order
+            cur = torch.cuda.current_stream()
+            for st in mb_streams:
+                st.wait_stream(cur)
+            plans = [None] * nmb
+            for i in range(nmb):
+                with torch.cuda.stream(mb_streams[i]):
+                    plans[i] = peps[i].plan(mb_ids[i])
+            for i in range(nmb):
+                with torch.cuda.stream(mb_streams[i]):
+                    peps[i].forward(plans[i], mb_x[i], out=mb_y[i])
+            for i in range(nmb):
+                with torch.cuda.stream(mb_streams[i]):
+                    peps[i].grad_input(plans[i], mb_dy[i], out=mb_dx[i])
+            for st in mb_streams:
+                cur.wait_stream(st)
+            return y_all, dx_all
 
         def step_nccl():
             plan = ep.plan(ids)
@@ -411,7 +450,8 @@ def gpu_arm(args):
         launches = 4 + (3 + 2 + 4 if pep is not None else 3 + 6)  # GEMMs + tile builders, routing sort, plan, exchange kernels
         result["device_status"] = native.device_status()
         if pep is not None:
-            result["ep_overflow"] = int(pep.overflow.item())
+            result["ep_overflow"] = int(sum(int(q.overflow.item()) for q in peps))
+            result["micro_batches"] = nmb
             parallelism = f"ep{world} (experts sharded; dispatch/combine by peer-memory kernels over NVLink, NCCL only for counts and fences)"
         else:
             parallelism = f"ep{world} (experts sharded, NCCL all-to-all dispatch/combine)"
@@ -470,6 +510,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", type=int, default=1,
+                    help="multi-GPU peer exchange: micro-batches per step (exchange of one overlaps matmuls of another)")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="multi-GPU row exchange: this library's peer-memory kernels, or NCCL all-to-all")
     ap.add_argument("--profile", action="store_true",

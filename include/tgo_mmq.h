@@ -119,11 +119,13 @@ int64_t tgo_route_workspace_bytes(int64_t n_pairs, int64_t num_experts);
  * (pair index = token * top_k + slot); outputs: sorted_to_pair int32[n_pairs] (pair held by each
  * sorted row), pair_to_sorted int32[n_pairs] (its inverse; -1 for an out-of-range id),
  * expert_indices int64[E] = 0..E-1 and expert_offsets int32[E] = cumulative end rows: exactly the
- * metadata of validate_grouped_mmq (csrc/mmq_hip.cu:325-406).  Device prefix sum; counterpart of
+ * metadata of validate_grouped_mmq (csrc/mmq_hip.cu:325-406); expert_counts int32[E] (may be null)
+ * = pairs per expert.  Device prefix sum; counterpart of
  * the reference's only device scan, grouped_mmq_build_row_tasks (csrc/mmq_core.cuh:516-571). */
 int tgo_route_sort(const int32_t* expert_ids, int64_t n_pairs, int64_t num_experts,
                    int32_t* sorted_to_pair, int32_t* pair_to_sorted, int64_t* expert_indices,
-                   int32_t* expert_offsets, void* workspace, int64_t workspace_bytes, void* stream);
+                   int32_t* expert_offsets, int32_t* expert_counts, void* workspace,
+                   int64_t workspace_bytes, void* stream);
 
 /* dst[r][:] = src[index[r] / divisor][:] for bf16 rows of `width` (a multiple of 8); with
  * index = sorted_to_pair and divisor = top_k this builds the expert-sorted activation rows. */

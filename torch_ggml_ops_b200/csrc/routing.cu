@@ -41,7 +41,8 @@ __global__ void __launch_bounds__(kRouteBlock) route_count_kernel(const int32_t*
 // block_counts[b][e] becomes the first sorted row of block b's pairs for expert e.
 __global__ void __launch_bounds__(1024) route_scan_kernel(int32_t* __restrict__ block_counts, int num_blocks,
                                                           int num_experts, int64_t* __restrict__ expert_indices,
-                                                          int32_t* __restrict__ expert_offsets) {
+                                                          int32_t* __restrict__ expert_offsets,
+                                                          int32_t* __restrict__ expert_counts) {
     __shared__ int32_t totals[kRouteMaxExperts];
     __shared__ int32_t warp_sums[32];
     for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
@@ -84,6 +85,7 @@ __global__ void __launch_bounds__(1024) route_scan_kernel(int32_t* __restrict__ 
             totals[e] = before;                    // first sorted row of expert e
             expert_offsets[e] = before + v;        // cumulative end row
             expert_indices[e] = e;
+            if (expert_counts != nullptr) expert_counts[e] = v;
         }
         carry += warp_sums[nwarps - 1];
         __syncthreads();
@@ -248,8 +250,8 @@ int64_t tgo_route_workspace_bytes(int64_t n_pairs, int64_t num_experts) {
 }
 
 int tgo_route_sort(const int32_t* expert_ids, int64_t n_pairs, int64_t num_experts, int32_t* sorted_to_pair,
-                   int32_t* pair_to_sorted, int64_t* expert_indices, int32_t* expert_offsets, void* workspace,
-                   int64_t workspace_bytes, void* stream) {
+                   int32_t* pair_to_sorted, int64_t* expert_indices, int32_t* expert_offsets, int32_t* expert_counts,
+                   void* workspace, int64_t workspace_bytes, void* stream) {
     if (expert_ids == nullptr || sorted_to_pair == nullptr || pair_to_sorted == nullptr || expert_indices == nullptr ||
         expert_offsets == nullptr || workspace == nullptr)
         return route_fail(TGO_E_ARG, "null pointer");
@@ -263,7 +265,7 @@ int tgo_route_sort(const int32_t* expert_ids, int64_t n_pairs, int64_t num_exper
     const int blocks = (n + kRouteBlock - 1) / kRouteBlock;
     int32_t* counts = static_cast<int32_t*>(workspace);
     route_count_kernel<<<blocks, kRouteBlock, E * sizeof(int32_t), s>>>(expert_ids, n, E, counts);
-    route_scan_kernel<<<1, 1024, 0, s>>>(counts, blocks, E, expert_indices, expert_offsets);
+    route_scan_kernel<<<1, 1024, 0, s>>>(counts, blocks, E, expert_indices, expert_offsets, expert_counts);
     route_scatter_kernel<<<blocks, kRouteBlock, E * sizeof(int32_t), s>>>(expert_ids, n, E, counts, sorted_to_pair,
                                                                          pair_to_sorted);
     return launch_check("routing kernel launch failed");

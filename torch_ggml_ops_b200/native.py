@@ -29,7 +29,7 @@ SIGNATURES = {
     "tgo_grouped_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
     "tgo_grouped_dx": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
     "tgo_route_workspace_bytes": (_i64, [_i64, _i64]),
-    "tgo_route_sort": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "tgo_route_sort": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
     "tgo_gather_rows": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _vp]),
     "tgo_combine_rows": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tgo_quantize_q8": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
@@ -144,20 +144,24 @@ def grouped_fwd_noalloc(x, w0, w1, y0, y1, expert_indices, expert_offsets, num_e
           "tgo_grouped_fwd_noalloc")
 
 
-def route_sort(expert_ids, num_experts, stream=None):
+def route_sort(expert_ids, num_experts, stream=None, out=None):
     """Device counting sort of routed pairs by expert.  ``expert_ids``: int32 [n_pairs] on the GPU.
-    Returns (sorted_to_pair, pair_to_sorted, expert_indices int64 [E], expert_offsets int32 [E])."""
+    Returns (sorted_to_pair, pair_to_sorted, expert_indices int64 [E], expert_offsets int32 [E]).
+    ``out``: optional dict of preallocated tensors (keys s2p, p2s, ei, eo, counts, ws); with a
+    ``counts`` entry the per-expert pair counts are written there too."""
     import torch
 
     n = expert_ids.numel()
     dev = expert_ids.device
-    s2p = torch.empty(n, dtype=torch.int32, device=dev)
-    p2s = torch.empty(n, dtype=torch.int32, device=dev)
-    ei = torch.empty(num_experts, dtype=torch.int64, device=dev)
-    eo = torch.empty(num_experts, dtype=torch.int32, device=dev)
-    ws = torch.empty(lib().tgo_route_workspace_bytes(n, num_experts), dtype=torch.uint8, device=dev)
-    check(lib().tgo_route_sort(_ptr(expert_ids), n, num_experts, _ptr(s2p), _ptr(p2s), _ptr(ei), _ptr(eo), _ptr(ws),
-                               ws.numel(), _stream(stream)), "tgo_route_sort")
+    out = {} if out is None else out
+    s2p = out.get("s2p") if "s2p" in out else torch.empty(n, dtype=torch.int32, device=dev)
+    p2s = out.get("p2s") if "p2s" in out else torch.empty(n, dtype=torch.int32, device=dev)
+    ei = out.get("ei") if "ei" in out else torch.empty(num_experts, dtype=torch.int64, device=dev)
+    eo = out.get("eo") if "eo" in out else torch.empty(num_experts, dtype=torch.int32, device=dev)
+    ws = out.get("ws") if "ws" in out else torch.empty(lib().tgo_route_workspace_bytes(n, num_experts),
+                                                        dtype=torch.uint8, device=dev)
+    check(lib().tgo_route_sort(_ptr(expert_ids), n, num_experts, _ptr(s2p), _ptr(p2s), _ptr(ei), _ptr(eo),
+                               _ptr(out.get("counts")), _ptr(ws), ws.numel(), _stream(stream)), "tgo_route_sort")
     return s2p, p2s, ei, eo
 
 
@@ -196,20 +200,22 @@ def _ptr_array(ptrs):
     return (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
 
 
-def ep_plan(counts_all, my_rank, expert_ids, pair_to_sorted, capacity, stream=None):
+def ep_plan(counts_all, my_rank, expert_ids, pair_to_sorted, capacity, stream=None, out=None):
     """Destination of every routed pair and the local group metadata; see ``tgo_ep_plan``.
     ``counts_all``: int32 [world, E] on the GPU.  Returns (dst_rank, dst_row, local_indices,
-    local_offsets, overflow_flag)."""
+    local_offsets, overflow_flag).  ``out``: optional dict of preallocated tensors (keys dst_rank,
+    dst_row, li, lo, scratch, overflow; the overflow flag is then sticky)."""
     import torch
 
     world, E = counts_all.shape
     n, dev = expert_ids.numel(), expert_ids.device
-    dst_rank = torch.empty(n, dtype=torch.int32, device=dev)
-    dst_row = torch.empty(n, dtype=torch.int32, device=dev)
-    li = torch.empty(E // world, dtype=torch.int64, device=dev)
-    lo = torch.empty(E // world, dtype=torch.int32, device=dev)
-    scratch = torch.empty(2 * E, dtype=torch.int32, device=dev)
-    overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = {} if out is None else out
+    dst_rank = out["dst_rank"] if "dst_rank" in out else torch.empty(n, dtype=torch.int32, device=dev)
+    dst_row = out["dst_row"] if "dst_row" in out else torch.empty(n, dtype=torch.int32, device=dev)
+    li = out["li"] if "li" in out else torch.empty(E // world, dtype=torch.int64, device=dev)
+    lo = out["lo"] if "lo" in out else torch.empty(E // world, dtype=torch.int32, device=dev)
+    scratch = out["scratch"] if "scratch" in out else torch.empty(2 * E, dtype=torch.int32, device=dev)
+    overflow = out["overflow"] if "overflow" in out else torch.zeros(1, dtype=torch.int32, device=dev)
     check(lib().tgo_ep_plan(_ptr(counts_all), world, E, my_rank, _ptr(expert_ids), _ptr(pair_to_sorted), n, capacity,
                             _ptr(dst_rank), _ptr(dst_row), _ptr(li), _ptr(lo), _ptr(scratch), _ptr(overflow),
                             _stream(stream)), "tgo_ep_plan")

@@ -68,6 +68,7 @@ class PeerExpertParallel:
         self.ws = torch.empty(native.grouped_workspace_bytes(self.cap, self.EL), dtype=torch.uint8, device=dev)
         self._token = torch.zeros(1, dtype=torch.int32, device=dev)
         self.overflow = None
+        self._plan_bufs = None   # routing outputs are reused from step to step (stream-ordered)
 
     # ------------------------------------------------------------------ ordering between ranks
     def _fence(self) -> None:
@@ -77,34 +78,55 @@ class PeerExpertParallel:
 
     # ------------------------------------------------------------------ routing
     def plan(self, topk_ids: torch.Tensor):
-        """``topk_ids``: integer [tokens, top_k] global expert ids on this rank's GPU."""
-        flat = topk_ids.reshape(-1).to(torch.int32)
-        _, p2s, _, ends = native.route_sort(flat, self.E)
-        counts = torch.diff(ends, prepend=ends.new_zeros(1))
+        """``topk_ids``: integer [tokens, top_k] global expert ids on this rank's GPU (int32 avoids a
+        conversion).  The returned plan refers to buffers that the next call of ``plan`` overwrites."""
+        flat = topk_ids.reshape(-1)
+        if flat.dtype != torch.int32:
+            flat = flat.to(torch.int32)
+        n = flat.numel()
+        if self._plan_bufs is None or self._plan_bufs["n"] != n:
+            dev, i32 = self.device, torch.int32
+            self._plan_bufs = {
+                "n": n,
+                "s2p": torch.empty(n, dtype=i32, device=dev), "p2s": torch.empty(n, dtype=i32, device=dev),
+                "ei": torch.empty(self.E, dtype=torch.int64, device=dev), "eo": torch.empty(self.E, dtype=i32, device=dev),
+                "counts": torch.empty(self.E, dtype=i32, device=dev),
+                "ws": torch.empty(native.lib().tgo_route_workspace_bytes(n, self.E), dtype=torch.uint8, device=dev),
+                "counts_all": torch.empty(self.world, self.E, dtype=i32, device=dev),
+                "dst_rank": torch.empty(n, dtype=i32, device=dev), "dst_row": torch.empty(n, dtype=i32, device=dev),
+                "li": torch.empty(self.EL, dtype=torch.int64, device=dev), "lo": torch.empty(self.EL, dtype=i32, device=dev),
+                "scratch": torch.empty(2 * self.E, dtype=i32, device=dev),
+                "overflow": torch.zeros(1, dtype=i32, device=dev),
+            }
+        b = self._plan_bufs
+        _, p2s, _, _ = native.route_sort(flat, self.E, out=b)
         if self.world > 1:
-            counts_all = torch.empty(self.world, self.E, dtype=torch.int32, device=self.device)
-            dist.all_gather_into_tensor(counts_all, counts, group=self.group)
+            counts_all = b["counts_all"]
+            dist.all_gather_into_tensor(counts_all, b["counts"], group=self.group)
         else:
-            counts_all = counts.reshape(1, self.E)
-        dst_rank, dst_row, li, lo, overflow = native.ep_plan(counts_all.contiguous(), self.rank, flat, p2s, self.cap)
+            counts_all = b["counts"].reshape(1, self.E)
+        dst_rank, dst_row, li, lo, overflow = native.ep_plan(counts_all, self.rank, flat, p2s, self.cap, out=b)
         self.overflow = overflow  # device flag: a row did not fit in `capacity_rows` (read it when convenient)
         return {"top_k": topk_ids.shape[1], "dst_rank": dst_rank, "dst_row": dst_row, "indices": li, "offsets": lo}
 
     # ------------------------------------------------------------------ forward
-    def forward(self, plan, x_tokens: torch.Tensor) -> torch.Tensor:
-        """[tokens, K] bf16 -> [tokens * top_k, N]: every routed pair's expert projection."""
+    def forward(self, plan, x_tokens: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """[tokens, K] bf16 -> [tokens * top_k, N]: every routed pair's expert projection
+        (written to ``out`` when given)."""
         k = plan["top_k"]
         native.ep_dispatch(x_tokens, k, plan["dst_rank"], plan["dst_row"], self.peers["x_in"])
         self._fence()
         native.grouped_fwd(self.buf["x_in"], self.weight, None, self.buf["y_out"], None, plan["indices"],
                            plan["offsets"], self.EL, self.cap, self.N, self.K, self.qt, self.ws)
         self._fence()
-        y = torch.empty(x_tokens.shape[0] * k, self.N, dtype=torch.bfloat16, device=self.device)
+        y = out if out is not None else torch.empty(x_tokens.shape[0] * k, self.N, dtype=torch.bfloat16,
+                                                     device=self.device)
         native.ep_pull(self.peers["y_out"], plan["dst_rank"], plan["dst_row"], y, 1)
         return y
 
     # ------------------------------------------------------------------ input gradient
-    def grad_input(self, plan, dy_pairs: torch.Tensor, weights: torch.Tensor | None = None) -> torch.Tensor:
+    def grad_input(self, plan, dy_pairs: torch.Tensor, weights: torch.Tensor | None = None,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
         """[tokens * top_k, N] cotangents per routed pair -> [tokens, K]: dX summed over the top-k
         slots of each token (optionally weighted), fp32 accumulation, one bf16 rounding."""
         k = plan["top_k"]
@@ -113,7 +135,8 @@ class PeerExpertParallel:
         native.grouped_dx(self.buf["dy_in"], None, self.weight, None, self.buf["dx_out"], plan["indices"],
                           plan["offsets"], self.EL, self.cap, self.N, self.K, self.qt, self.ws)
         self._fence()
-        dx = torch.empty(dy_pairs.shape[0] // k, self.K, dtype=torch.bfloat16, device=self.device)
+        dx = out if out is not None else torch.empty(dy_pairs.shape[0] // k, self.K, dtype=torch.bfloat16,
+                                                      device=self.device)
         w = None if weights is None else weights.reshape(-1).float().contiguous()
         native.ep_pull(self.peers["dx_out"], plan["dst_rank"], plan["dst_row"], dx, k, w)
         return dx
