@@ -334,13 +334,18 @@ def gpu_arm(args):
         d2h = yh.numel() * 2 + dxh.numel() * 2
         launches = 4  # tile builder + GEMM, forward and backward
         peaks = json.load(open(ROOT / "MEASURED_PEAKS.json")) if (ROOT / "MEASURED_PEAKS.json").exists() else None
-        peak_tf = peaks["bf16_tflops"] if peaks else 1590.0
+        # The launches are timed back to back inside a power-capped loop (a second of the same load
+        # runs first), so the sustained cuBLAS figure is the denominator; the burst one is given too.
+        peak_tf = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) if peaks else 1400.0
+        burst_tf = peaks["bf16_tflops"] if peaks else 1590.0
         peak_hbm = peaks["hbm_gbs"] if peaks else 6650.0
         flops_dir = 2.0 * R * N * K
         bytes_dir = R * K * 2 + R * N * 2 + w.numel()  # activations once, packed experts once, outputs once
         roof = lambda ms: {  # noqa: E731
             "bound": "tensor", "achieved": flops_dir / (ms * 1e-3) / 1e12, "peak": peak_tf, "unit": "TFLOP/s",
-            "frac": flops_dir / (ms * 1e-3) / 1e12 / peak_tf, "peak_source": "measured (burst)" if peaks else "fallback",
+            "frac": flops_dir / (ms * 1e-3) / 1e12 / peak_tf,
+            "peak_source": "measured, sustained bf16 cuBLAS (MEASURED_PEAKS.json)" if peaks else "fallback",
+            "frac_of_burst_peak": flops_dir / (ms * 1e-3) / 1e12 / burst_tf, "burst_peak": burst_tf,
             "hbm_gbs": bytes_dir / (ms * 1e-3) / 1e9, "hbm_frac": bytes_dir / (ms * 1e-3) / 1e9 / peak_hbm,
             "ms_per_launch": ms}
         result["roofline"] = dict(roof(fwd_ms), kernel="mmq_gemm_kernel<Q4_K, forward> (+ tile builder)",

@@ -85,7 +85,7 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 
 // bf16 matrix [rows][inner], row-major; boxes of 64 columns x {256,128,64,32,16} rows with the
 // 128-byte swizzle.  Out-of-range rows / columns read as zero.
-static int make_act_maps(ActMaps& maps, const void* base, int64_t rows, int64_t inner) {
+static int encode_act_maps(ActMaps& maps, const void* base, int64_t rows, int64_t inner) {
     // The encoder is a driver entry point and needs a context bound to the calling thread; a
     // thread that has only inherited its device (an autograd worker, say) may not have one yet.
     int dev = 0;
@@ -109,8 +109,8 @@ static int make_act_maps(ActMaps& maps, const void* base, int64_t rows, int64_t 
 
 // Packed weight tensor [total_rows][row_bytes] as up to 8 byte-typed 2-D maps, one per alignment
 // class of its rows (see WgtMaps).  Box = one block window (copy_bytes) x box_rows / P rows.
-static int make_wgt_maps(WgtMaps& maps, const void* base, int64_t total_rows, int64_t row_bytes, int copy_bytes,
-                         int box_rows, int& classes, int& classes_log2) {
+static int encode_wgt_maps(WgtMaps& maps, const void* base, int64_t total_rows, int64_t row_bytes, int copy_bytes,
+                           int box_rows, int& classes, int& classes_log2) {
     auto encode = encode_fn();
     if (encode == nullptr) return fail(TGO_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     int g = 16;
@@ -138,6 +138,68 @@ static int make_wgt_maps(WgtMaps& maps, const void* base, int64_t total_rows, in
         if (r != CUDA_SUCCESS)
             return fail(TGO_E_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", static_cast<int>(r));
     }
+    return TGO_OK;
+}
+
+// A tensor map only encodes (address, shape, box): it can be reused for as long as those are the
+// same, whatever the buffer holds.  Encoding takes a few microseconds per map and a call needs up
+// to 26 of them, so each thread remembers the last few (weights come back with every call,
+// activations whenever the caller's allocator hands out the same block again).
+template <typename Maps>
+struct MapCache {
+    struct Entry {
+        const void* base = nullptr;
+        int64_t a = 0, b = 0, c = 0;
+        int dev = -1, classes = 0, classes_log2 = 0;
+        Maps maps;
+    };
+    static constexpr int kEntries = 8;
+    Entry e[kEntries];
+    int next = 0;
+    Entry* find(const void* base, int64_t a, int64_t b, int64_t c, int dev) {
+        for (int i = 0; i < kEntries; ++i)
+            if (e[i].base == base && e[i].a == a && e[i].b == b && e[i].c == c && e[i].dev == dev) return &e[i];
+        return nullptr;
+    }
+    Entry* slot() {
+        Entry* r = &e[next];
+        next = (next + 1) % kEntries;
+        return r;
+    }
+};
+
+static int make_act_maps(ActMaps& maps, const void* base, int64_t rows, int64_t inner) {
+    static thread_local MapCache<ActMaps> cache;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = -2;
+    if (auto* hit = cache.find(base, rows, inner, 0, dev)) {
+        maps = hit->maps;
+        return TGO_OK;
+    }
+    const int rc = encode_act_maps(maps, base, rows, inner);
+    if (rc != TGO_OK) return rc;
+    auto* s = cache.slot();
+    s->base = base; s->a = rows; s->b = inner; s->c = 0; s->dev = dev; s->maps = maps;
+    return TGO_OK;
+}
+
+static int make_wgt_maps(WgtMaps& maps, const void* base, int64_t total_rows, int64_t row_bytes, int copy_bytes,
+                         int box_rows, int& classes, int& classes_log2) {
+    static thread_local MapCache<WgtMaps> cache;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = -2;
+    const int64_t shape_key = (static_cast<int64_t>(copy_bytes) << 16) | box_rows;
+    if (auto* hit = cache.find(base, total_rows, row_bytes, shape_key, dev)) {
+        maps = hit->maps;
+        classes = hit->classes;
+        classes_log2 = hit->classes_log2;
+        return TGO_OK;
+    }
+    const int rc = encode_wgt_maps(maps, base, total_rows, row_bytes, copy_bytes, box_rows, classes, classes_log2);
+    if (rc != TGO_OK) return rc;
+    auto* s = cache.slot();
+    s->base = base; s->a = total_rows; s->b = row_bytes; s->c = shape_key; s->dev = dev;
+    s->classes = classes; s->classes_log2 = classes_log2; s->maps = maps;
     return TGO_OK;
 }
 
