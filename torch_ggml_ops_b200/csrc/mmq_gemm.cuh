@@ -41,15 +41,29 @@ enum : int { kFwd = 0, kBwd = 1 };
 constexpr int kTileM = 128;          // weight-side extent of one tile (TMEM lanes)
 constexpr int kTileTok = 256;        // most tokens per tile (TMEM columns of one accumulator)
 constexpr int kStepK = 64;           // reduction elements per pipeline step (one swizzle row)
-constexpr int kActTileBytes = kTileTok * 128;
 constexpr int kWgtTileBytes = kTileM * 128;
+// Ring depths.  One CTA: 4 activation stages of 32 KB, up to 3 decoded-weight stages.  CTA pair:
+// each CTA stages only its half of the tokens (16 KB), which buys deeper rings from the same
+// shared memory: the credit of a stage is away for a TMA round trip plus the UMMAs plus two
+// barrier hops (about 2500 cycles), so depth, not bandwidth, is what keeps the tensor pipe fed.
 #ifndef TGO_ACT_STAGES
 #define TGO_ACT_STAGES 4
 #endif
 #ifndef TGO_WGT_STAGES_MAX
 #define TGO_WGT_STAGES_MAX 3
 #endif
-constexpr int kActStages = TGO_ACT_STAGES;
+#ifndef TGO_PAIR_ACT_STAGES
+#define TGO_PAIR_ACT_STAGES 6
+#endif
+#ifndef TGO_PAIR_WGT_STAGES_MAX
+#define TGO_PAIR_WGT_STAGES_MAX 4
+#endif
+#ifndef TGO_PAIR_RAW_STAGES_FWD
+#define TGO_PAIR_RAW_STAGES_FWD 3
+#endif
+#ifndef TGO_PAIR_RAW_STAGES_BWD
+#define TGO_PAIR_RAW_STAGES_BWD 6
+#endif
 constexpr int kDecodeWarps = 8;        // warps of one decode group (256 threads x 32 weights = one step)
 constexpr int kDecodeGroups = 2;       // groups take alternate steps, so two steps decode at once
 constexpr int kFirstDecodeWarp = 4;
@@ -99,18 +113,31 @@ struct GemmArgs {
     int wgt_row_bytes;                   // (K / 256) * block bytes
 };
 
-template <int QT, int MODE>
+// CG = 1: one CTA per tile of 128 weight rows.  CG = 2: a cluster of two CTAs works on 256 weight
+// rows and one token tile with cta_group::2 UMMAs (each CTA decodes its own 128 rows and stages
+// half of the tokens; the leader CTA issues).
+template <int QT, int MODE, int CG>
 struct GemmCfg {
     using Fmt = BlockFmt<QT>;
+    static constexpr int kActRows = kTileTok / CG;              // token rows staged by one CTA
+    static constexpr int kActTileBytes = kActRows * 128;
+    static constexpr int kActStages = CG == 2 ? TGO_PAIR_ACT_STAGES : TGO_ACT_STAGES;
+    static constexpr int kWgtStagesMax = CG == 2 ? TGO_PAIR_WGT_STAGES_MAX : TGO_WGT_STAGES_MAX;
+    static constexpr int kTokPad = CG == 2 ? 32 : 16;           // token padding of a tile (UMMA N granularity)
     static constexpr int kRawRows = MODE == kFwd ? 128 : 64;    // block windows per raw stage
-    static constexpr int kRawStages = MODE == kFwd ? 2 : 4;
+    // pair: as many raw stages as fit in about 56 KB (the raw ring has to cover an HBM round trip)
+    static constexpr int kRawFit = 57344 / (kRawRows * Fmt::kCopy);
+    static constexpr int kRawMaxPair = MODE == kFwd ? TGO_PAIR_RAW_STAGES_FWD : TGO_PAIR_RAW_STAGES_BWD;
+    static constexpr int kRawStages = CG == 2 ? (kRawFit >= kRawMaxPair ? kRawMaxPair : (kRawFit < 2 ? 2 : kRawFit))
+                                              : (MODE == kFwd ? 2 : 4);
     static constexpr int kRawStageBytes = kRawRows * Fmt::kCopy;
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kGridBytes = QT == QT_IQ2_S ? 8192 : 0;
     static constexpr int kFixed = 1024 /*alignment slack*/ + 512 /*barriers etc.*/ + 128 /*read slack*/ + kEpiStageBytes +
                                   kActStages * kActTileBytes + kRawBytes + kGridBytes;
     static constexpr int kWgtStagesFit = (kSmemLimit - kFixed) / kWgtTileBytes;
-    static constexpr int kWgtStages = kWgtStagesFit >= TGO_WGT_STAGES_MAX ? TGO_WGT_STAGES_MAX : kWgtStagesFit;
+    static constexpr int kWgtStagesCap = kWgtStagesMax < kActStages ? kWgtStagesMax : kActStages;
+    static constexpr int kWgtStages = kWgtStagesFit >= kWgtStagesCap ? kWgtStagesCap : kWgtStagesFit;
     static_assert(kWgtStages >= 2, "shared memory budget");
     static constexpr int kSmemBytes = kFixed + kWgtStages * kWgtTileBytes;
 };
@@ -120,9 +147,10 @@ struct TileInfo {
 };
 
 
-template <int MODE>
+// `mtiles` / `mtiles_set` count tiles of CG * 128 weight rows; `rank` is the CTA's rank in its pair.
+template <int MODE, int CG>
 __device__ __forceinline__ bool load_tile(const GemmArgs& a, int tile, int mtiles, int mtiles_set,
-                                          TileInfo& t) {
+                                          int rank, TileInfo& t) {
     const int task = tile / mtiles;
     const int mt = tile - task * mtiles;
     if (a.tasks != nullptr) {
@@ -135,13 +163,14 @@ __device__ __forceinline__ bool load_tile(const GemmArgs& a, int tile, int mtile
         t.row0 = task * a.dense_tok;
         t.ntok = min(a.dense_tok, a.rows - t.row0);
     }
-    t.ntok_pad = (t.ntok + 15) & ~15;
+    constexpr int kPad = CG == 2 ? 32 : 16;
+    t.ntok_pad = (t.ntok + kPad - 1) & ~(kPad - 1);
     if (MODE == kFwd) {
         t.set = mt / mtiles_set;
-        t.m0 = (mt - t.set * mtiles_set) * kTileM;
+        t.m0 = ((mt - t.set * mtiles_set) * CG + rank) * kTileM;
     } else {
         t.set = 0;
-        t.m0 = mt * kTileM;
+        t.m0 = (mt * CG + rank) * kTileM;
     }
     return t.ntok > 0;
 }
@@ -163,12 +192,18 @@ __device__ __forceinline__ bool all_wait(uint32_t bar, uint32_t parity, volatile
     return __all_sync(0xFFFFFFFFu, ok) != 0;
 }
 
-template <int QT, int MODE>
+template <int QT, int MODE, int CG>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
-    using Cfg = GemmCfg<QT, MODE>;
+    using Cfg = GemmCfg<QT, MODE, CG>;
     using Fmt = BlockFmt<QT>;
-    constexpr int NA = Cfg::kWgtStages, NB = kActStages, NR = Cfg::kRawStages;
+    constexpr int NA = Cfg::kWgtStages, NB = Cfg::kActStages, NR = Cfg::kRawStages;
+    constexpr int kActTileBytes = Cfg::kActTileBytes;
+    // CTA pair: rank 0 (the leader) owns the barriers both CTAs feed (full, acc_empty) and issues
+    // the UMMAs; every CTA owns the barriers only it waits on (done, raw, acc_full).
+    const int rank = CG == 2 ? static_cast<int>(cluster_ctarank()) : 0;
+    const int cta = CG == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int ncta = CG == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
     static_assert(NA <= NB, "the decoded-weight ring may not be deeper than the step ring");
 
     extern __shared__ uint8_t smem_dyn[];
@@ -204,7 +239,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     const int N = args.out_features, K = args.in_features;
     const int nkb = K >> 8;
     // tile space
-    const int mtiles_set = MODE == kFwd ? (N + kTileM - 1) / kTileM : K / kTileM;
+    const int mtiles_set = MODE == kFwd ? (N + CG * kTileM - 1) / (CG * kTileM) : K / (CG * kTileM);
     const int mtiles = MODE == kFwd ? mtiles_set * args.nsets : mtiles_set;
     const int steps_set = MODE == kFwd ? K / kStepK : (N + kStepK - 1) / kStepK;
     const int nsteps = MODE == kFwd ? steps_set : steps_set * args.nsets;
@@ -212,12 +247,17 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     const long long total_tiles = static_cast<long long>(ntasks) * mtiles;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NB; ++i) { mbar_init(bar_full + 8 * i, 1 + kDecodeWarps); mbar_init(bar_done + 8 * i, 1); }
+        // full: the leader's activation producer (with the byte count of both halves) - or both
+        // producers when they copy with plain loads - and the decode warps of every CTA
+        for (int i = 0; i < NB; ++i) {
+            mbar_init(bar_full + 8 * i, (args.use_tma ? 1 : CG) + CG * kDecodeWarps);
+            mbar_init(bar_done + 8 * i, 1);
+        }
         for (int i = 0; i < NR; ++i) {
             mbar_init(bar_raw_full + 8 * i, 1);
             mbar_init(bar_raw_empty + 8 * i, MODE == kFwd ? kDecodeWarps * kDecodeGroups : kDecodeWarps);
         }
-        for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, 4 * CG); }
         *abort_word = 0;
         mbar_fence_init();
     }
@@ -226,13 +266,21 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         for (int i = threadIdx.x; i < 1024; i += kGemmThreads) gdst[i] = args.iq2s_grid[i];
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-        tmem_relinquish();
+        if (CG == 2) {
+            tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before_sync();
-    __syncthreads();
+    if (CG == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // barriers of the leader, as seen from this CTA
+    const uint32_t lead_full = CG == 2 ? map_to_cta(bar_full, 0) : bar_full;
+    const uint32_t lead_acc_empty = CG == 2 ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
 
     if (warp == 0) {
         // ------------------------------------------------------------ activation producer
@@ -242,23 +290,28 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     for (int b = 0; b < kNumBoxes; ++b) prefetch_tmap(&args.act_maps[s].box[b]);
                 uint32_t it = 0;
                 bool ok = true;
-                for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                     TileInfo t;
-                    if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+                    if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                     for (int step = 0; step < nsteps; ++step, ++it) {
                         const uint32_t s = it % NB, ph = (it / NB) & 1u;
                         if (!mbar_wait(bar_done + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty)) { ok = false; break; }
                         const int set = MODE == kFwd ? 0 : step / steps_set;
                         const int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
-                        const uint32_t bar = bar_full + 8 * s;
-                        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(t.ntok_pad) * 128u);
+                        // the leader announces the bytes of the whole tile; each CTA copies its share
+                        // of the token rows (all of them, or its half) and the bytes count on the
+                        // leader's barrier
+                        const uint32_t bar = lead_full + 8 * s;
+                        if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, static_cast<uint32_t>(t.ntok_pad) * 128u);
                         uint32_t dst = act_s + s * kActTileBytes;
-                        int row = t.row0, rem = t.ntok_pad;
+                        int rem = t.ntok_pad / CG;
+                        int row = t.row0 + rank * rem;
 #pragma unroll
                         for (int b = 0; b < kNumBoxes; ++b) {
                             const int h = 256 >> b;
-                            if (rem >= h) {
-                                tma_load_2d(dst, &args.act_maps[set].box[b], bar, red0, row);
+                            if (h <= Cfg::kActRows && rem >= h) {
+                                if (CG == 2) tma_load_2d_pair(dst, &args.act_maps[set].box[b], bar, red0, row);
+                                else tma_load_2d(dst, &args.act_maps[set].box[b], bar, red0, row);
                                 dst += h * 128;
                                 row += h;
                                 rem -= h;
@@ -273,9 +326,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             uint32_t it = 0;
             bool ok = true;
             const int red_total = MODE == kFwd ? K : N;
-            for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 for (int step = 0; step < nsteps; ++step, ++it) {
                     const uint32_t s = it % NB, ph = (it / NB) & 1u;
                     if (!lane0_wait(bar_done + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty, lane)) { ok = false; break; }
@@ -283,9 +336,10 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     const int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
                     const __nv_bfloat16* src = args.act[set];
                     uint8_t* dst = act_g + s * kActTileBytes;
-                    for (int idx = lane; idx < t.ntok_pad * 8; idx += 32) {
+                    const int my_rows = t.ntok_pad / CG;
+                    for (int idx = lane; idx < my_rows * 8; idx += 32) {
                         const int r = idx >> 3, c = idx & 7;
-                        const long long grow = static_cast<long long>(t.row0) + r;
+                        const long long grow = static_cast<long long>(t.row0) + rank * my_rows + r;
                         alignas(16) __nv_bfloat16 v[8];
 #pragma unroll
                         for (int e = 0; e < 8; ++e) {
@@ -298,48 +352,80 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                    if (lane == 0) {
+                        if (CG == 2) mbar_arrive_cluster(lead_full + 8 * s); else mbar_arrive(bar_full + 8 * s);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ UMMA issuer (one thread)
-        if (lane == 0) {
-            uint32_t it = 0, tl = 0;
+        // This thread's instruction stream is the serial spine of the kernel: every step it waits,
+        // issues four UMMAs and one commit, each a dependent chain of its own.  The loop therefore
+        // keeps stage counters, barrier addresses and the low descriptor words as running values
+        // (one add per use) and builds nothing from scratch inside a step.
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version, SWIZZLE_128B
+            constexpr uint32_t kLboA = MODE == kFwd ? 16u : 8192u;                 // forward K-major, backward MN-major
+            constexpr uint32_t kStepA = (MODE == kFwd ? 32u : 2048u) >> 4;         // next 16 reduction elements of A
+            constexpr uint32_t kStepB = 32u >> 4;
+            // descriptors hold the address inside the CTA's shared memory (the same in both CTAs of a pair)
+            const uint32_t a_lo0 = ((wgt_s & 0x3FFFFu) >> 4) | ((kLboA >> 4) << 16);
+            const uint32_t b_lo0 = ((act_s & 0x3FFFFu) >> 4) | ((16u >> 4) << 16);
+            // the peer's copies of the barriers the commits signal
+            const uint32_t peer_done = CG == 2 ? map_to_cta(bar_done, 1) : 0u;
+            const uint32_t peer_acc_full = CG == 2 ? map_to_cta(bar_acc_full, 1) : 0u;
+            uint32_t a_lo = a_lo0, b_lo = b_lo0, sa = 0, sb = 0, ph = 0;
+            uint32_t full_bar = bar_full, done_bar = bar_done;
+            uint32_t tl = 0;
             bool ok = true;
             // the test of the next step's barrier is issued before this step's UMMAs, so its latency
             // overlaps their issue; a negative answer only means "ask again, blocking"
             bool ready = false;
-            for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
                 ++tl;
                 if (!mbar_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kAbortAccEmpty)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kTileTok;
                 const uint32_t idesc =
-                    umma_idesc_bf16(static_cast<uint32_t>(t.ntok_pad), MODE == kBwd ? 1u : 0u, 0u);
-                for (int step = 0; step < nsteps; ++step, ++it) {
-                    const uint32_t s = it % NB, ph = (it / NB) & 1u;
-                    if (!ready && !mbar_wait(bar_full + 8 * s, ph, abort_word, kAbortWgtFull)) { ok = false; break; }
-                    {
-                        const uint32_t nx = it + 1;
-                        ready = mbar_try_wait(bar_full + 8 * (nx % NB), (nx / NB) & 1u);
-                    }
-                    tc_fence_after_sync();
-                    const uint32_t wa = wgt_s + (it % NA) * kWgtTileBytes;
-                    const uint32_t ba = act_s + s * kActTileBytes;
+                    umma_idesc_bf16(static_cast<uint32_t>(t.ntok_pad), MODE == kBwd ? 1u : 0u, 0u, 128u * CG);
+                for (int step = 0; step < nsteps; ++step) {
+                    if (!ready && !mbar_wait(full_bar, ph, abort_word, kAbortWgtFull)) { ok = false; break; }
+                    const uint32_t cur_done = done_bar, cur_a = a_lo, cur_b = b_lo;
+                    // advance the rings (independent of the UMMAs below, so it overlaps their issue)
+                    a_lo += kWgtTileBytes >> 4;
+                    if (++sa == NA) { sa = 0; a_lo = a_lo0; }
+                    b_lo += kActTileBytes >> 4;
+                    full_bar += 8;
+                    done_bar += 8;
+                    if (++sb == NB) { sb = 0; b_lo = b_lo0; full_bar = bar_full; done_bar = bar_done; ph ^= 1u; }
+                    ready = mbar_try_wait(full_bar, ph);
+                    if (CG == 2) {
+                        umma_bf16_lohi_pair(d_tmem, cur_a, cur_b, kDescHi, idesc, step != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < kStepK / 16; ++kk) {
-                        const uint64_t adesc = MODE == kFwd ? umma_smem_desc(wa + kk * 32, 16, 1024)
-                                                            : umma_smem_desc(wa + kk * 2048, 8192, 1024);
-                        const uint64_t bdesc = umma_smem_desc(ba + kk * 32, 16, 1024);
-                        umma_bf16(d_tmem, adesc, bdesc, idesc, (step | kk) != 0 ? 1u : 0u);
+                        for (uint32_t kk = 1; kk < kStepK / 16; ++kk)
+                            umma_bf16_lohi_pair(d_tmem, cur_a + kk * kStepA, cur_b + kk * kStepB, kDescHi, idesc, 1u);
+                        umma_commit_pair(cur_done);
+                        umma_commit_pair(peer_done + (cur_done - bar_done));
+                    } else {
+                        umma_bf16_lohi(d_tmem, cur_a, cur_b, kDescHi, idesc, step != 0 ? 1u : 0u);
+#pragma unroll
+                        for (uint32_t kk = 1; kk < kStepK / 16; ++kk)
+                            umma_bf16_lohi(d_tmem, cur_a + kk * kStepA, cur_b + kk * kStepB, kDescHi, idesc, 1u);
+                        umma_commit(cur_done);
                     }
-                    umma_commit(bar_done + 8 * s);
                 }
-                if (ok) umma_commit(bar_acc_full + 8 * acc);
+                if (ok) {
+                    if (CG == 2) {
+                        umma_commit_pair(bar_acc_full + 8 * acc);
+                        umma_commit_pair(peer_acc_full + 8 * acc);
+                    } else {
+                        umma_commit(bar_acc_full + 8 * acc);
+                    }
+                }
             }
         }
     } else if (warp == 2) {
@@ -352,9 +438,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             constexpr int kRows = Cfg::kRawRows;
             for (int s = 0; s < args.nsets; ++s)
                 for (int c = 0; c < P; ++c) prefetch_tmap(&args.wgt_maps[s].cls[c]);
-            for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 const int nraw = MODE == kFwd ? nkb : nsteps;
                 for (int ri = 0; ri < nraw; ++ri, ++itr) {
                     const uint32_t r = itr % NR, ph = (itr / NR) & 1u;
@@ -386,8 +472,17 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         // stage (a super-block column of 128 rows) serves four steps, two per group; a thread
         // keeps its row and 32-weight half for the whole tile.  Backward: one raw stage (64 rows)
         // per step; a thread keeps its row slot and 32-weight group.
+        // A group owns two of the SM's four warp schedulers (a warp's scheduler is its index
+        // mod 4): the warps of one scheduler are then always in the same phase, so a group that
+        // waits is never starved of issue slots by the other group's arithmetic.
+#ifdef TGO_GROUPS_INTERLEAVED
         const int group = (warp - kFirstDecodeWarp) / kDecodeWarps;
         const int dt = threadIdx.x - (kFirstDecodeWarp + group * kDecodeWarps) * 32;  // 0..255
+#else
+        const int dw = warp - kFirstDecodeWarp;             // 0..15; kFirstDecodeWarp is a multiple of 4
+        const int group = (dw & 3) >> 1;
+        const int dt = (((dw >> 2) << 1) | (dw & 1)) * 32 + lane;  // 0..255 inside the group
+#endif
         const int row = MODE == kFwd ? dt >> 1 : dt >> 2;     // weight row inside the raw stage
         const int sub = MODE == kFwd ? dt & 1 : dt & 3;       // which 32 weights of the step's span
         // byte offsets of this thread's four 16-byte chunks inside a decoded tile (128B swizzle)
@@ -421,16 +516,16 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(bar_full + 8 * (it % NB));
+                if (CG == 2) mbar_arrive_cluster(lead_full + 8 * (it % NB)); else mbar_arrive(bar_full + 8 * (it % NB));
                 if (raw_bar_to_release != 0) mbar_arrive(raw_bar_to_release);
             }
             it += kDecodeGroups;
             return true;
         };
 
-        for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
             TileInfo t;
-            if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+            if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
             const long long gexp = static_cast<long long>(t.expert) * N;
             if (MODE == kFwd) {
                 const bool row_ok = t.m0 + row < N;
@@ -481,9 +576,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         const int quad = warp & 3;
         uint32_t tl = 0;
         const int mdim = MODE == kFwd ? N : K;
-        for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        for (long long tile = cta; tile < total_tiles; tile += ncta) {
             TileInfo t;
-            if (!load_tile<MODE>(args, static_cast<int>(tile), mtiles, mtiles_set, t)) continue;
+            if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
             const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
             ++tl;
             if (!all_wait(bar_acc_full + 8 * acc, aph, abort_word, kAbortAccFull)) break;
@@ -539,7 +634,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+            if (lane == 0) {
+                if (CG == 2) mbar_arrive_cluster(lead_acc_empty + 8 * acc); else mbar_arrive(bar_acc_empty + 8 * acc);
+            }
         }
     }
 
@@ -551,11 +648,13 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         for (int i = 0; i < 200; ++i) __nanosleep(1000);
     }
     tc_fence_before_sync();
-    __syncthreads();
+    // pair: neither CTA may leave (or free its TMEM) while the other can still signal its barriers
+    // or have UMMAs reading its shared memory
+    if (CG == 2) cluster_sync_all(); else __syncthreads();
     if (warp == 1) {
         __syncwarp();
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, kTmemCols);
+        if (CG == 2) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
     }
     if (threadIdx.x == 0 && *abort_word != 0 && args.status != nullptr)
         atomicCAS(args.status, 0, (*abort_word) | (static_cast<int>(blockIdx.x) << 8));

@@ -1,5 +1,6 @@
 // One translation unit per quant type (compile with -DTGO_QT=<ggml type id>): instantiates the
-// forward and backward GEMM kernels for that type and their launch function.
+// forward and backward GEMM kernels for that type, as single-CTA kernels and as CTA-pair
+// (cluster of two) kernels, and their launch functions.
 #include "mmq_launch.h"
 
 #ifndef TGO_QT
@@ -8,29 +9,90 @@
 
 namespace tgo {
 
-template <int QT, int MODE>
-static int launch_one(const GemmArgs& args, int grid, cudaStream_t stream) {
-    using Cfg = GemmCfg<QT, MODE>;
+template <int QT, int MODE, int CG>
+static cudaError_t configure() {
+    using Cfg = GemmCfg<QT, MODE, CG>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 64 && configured[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(mmq_gemm_kernel<QT, MODE, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    if (dev < 64) configured[dev] = true;
+    return cudaSuccess;
+}
+
+template <int QT, int MODE, int CG>
+static void fill_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute& attr, int grid, cudaStream_t stream) {
+    using Cfg = GemmCfg<QT, MODE, CG>;
+    cfg = cudaLaunchConfig_t{};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = CG;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+}
+
+template <int QT, int MODE, int CG>
+static int launch_one(const GemmArgs& args, int grid, cudaStream_t stream) {
+    cudaError_t e = configure<QT, MODE, CG>();
     if (e != cudaSuccess) return static_cast<int>(e);
-    if (dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(mmq_gemm_kernel<QT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg::kSmemBytes);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        configured[dev] = true;
+    if (CG == 1) {
+        mmq_gemm_kernel<QT, MODE, CG><<<grid, kGemmThreads, GemmCfg<QT, MODE, CG>::kSmemBytes, stream>>>(args);
+        return static_cast<int>(cudaGetLastError());
     }
-    mmq_gemm_kernel<QT, MODE><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(args);
-    return static_cast<int>(cudaGetLastError());
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    fill_config<QT, MODE, CG>(cfg, attr, grid, stream);
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, mmq_gemm_kernel<QT, MODE, CG>, args));
+}
+
+// Most CTA pairs of this kernel that can be resident at once on the current device (0: pairs
+// cannot be launched here).
+template <int QT, int MODE>
+static int max_pairs_one() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev < 64 && cached[dev] != 0) return cached[dev] > 0 ? cached[dev] : 0;
+    int n = 0;
+    if (configure<QT, MODE, 2>() == cudaSuccess) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr;
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        fill_config<QT, MODE, 2>(cfg, attr, sms & ~1, nullptr);
+        if (cudaOccupancyMaxActiveClusters(&n, mmq_gemm_kernel<QT, MODE, 2>, &cfg) != cudaSuccess) {
+            (void)cudaGetLastError();
+            n = 0;
+        }
+    } else {
+        (void)cudaGetLastError();
+    }
+    if (dev < 64) cached[dev] = n > 0 ? n : -1;
+    return n;
 }
 
 #define TGO_CAT2(a, b) a##b
 #define TGO_CAT(a, b) TGO_CAT2(a, b)
 
-int TGO_CAT(launch_gemm_, TGO_QT)(int mode, const GemmArgs& args, int grid, cudaStream_t stream) {
-    return mode == kFwd ? launch_one<TGO_QT, kFwd>(args, grid, stream)
-                        : launch_one<TGO_QT, kBwd>(args, grid, stream);
+int TGO_CAT(launch_gemm_, TGO_QT)(int mode, int cta_group, const GemmArgs& args, int grid, cudaStream_t stream) {
+    if (cta_group == 2)
+        return mode == kFwd ? launch_one<TGO_QT, kFwd, 2>(args, grid, stream)
+                            : launch_one<TGO_QT, kBwd, 2>(args, grid, stream);
+    return mode == kFwd ? launch_one<TGO_QT, kFwd, 1>(args, grid, stream)
+                        : launch_one<TGO_QT, kBwd, 1>(args, grid, stream);
+}
+
+int TGO_CAT(max_pairs_, TGO_QT)(int mode) {
+    return mode == kFwd ? max_pairs_one<TGO_QT, kFwd>() : max_pairs_one<TGO_QT, kBwd>();
 }
 
 }  // namespace tgo

@@ -8,6 +8,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -314,18 +315,39 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
 }
 
 // ------------------------------------------------------------------ GEMM dispatch
-static int dispatch_gemm(int qt, int mode, const GemmArgs& args, int grid, cudaStream_t stream) {
+static int dispatch_gemm(int qt, int mode, int cta_group, const GemmArgs& args, int grid, cudaStream_t stream) {
     int e;
     switch (qt) {
-        case QT_Q3_K: e = launch_gemm_11(mode, args, grid, stream); break;
-        case QT_Q4_K: e = launch_gemm_12(mode, args, grid, stream); break;
-        case QT_Q5_K: e = launch_gemm_13(mode, args, grid, stream); break;
-        case QT_Q6_K: e = launch_gemm_14(mode, args, grid, stream); break;
-        case QT_IQ2_S: e = launch_gemm_22(mode, args, grid, stream); break;
+        case QT_Q3_K: e = launch_gemm_11(mode, cta_group, args, grid, stream); break;
+        case QT_Q4_K: e = launch_gemm_12(mode, cta_group, args, grid, stream); break;
+        case QT_Q5_K: e = launch_gemm_13(mode, cta_group, args, grid, stream); break;
+        case QT_Q6_K: e = launch_gemm_14(mode, cta_group, args, grid, stream); break;
+        case QT_IQ2_S: e = launch_gemm_22(mode, cta_group, args, grid, stream); break;
         default: return fail(TGO_E_ARG, "unsupported quant_type: %d", qt);
     }
     if (e != 0) return cuda_fail(static_cast<cudaError_t>(e), "mmq_gemm_kernel launch");
     return TGO_OK;
+}
+
+static int max_pairs(int qt, int mode) {
+    switch (qt) {
+        case QT_Q3_K: return max_pairs_11(mode);
+        case QT_Q4_K: return max_pairs_12(mode);
+        case QT_Q5_K: return max_pairs_13(mode);
+        case QT_Q6_K: return max_pairs_14(mode);
+        case QT_IQ2_S: return max_pairs_22(mode);
+        default: return 0;
+    }
+}
+
+// 1: tiles of 128 weight rows on single CTAs (the default); 2: tiles of 256 rows on CTA pairs
+// (environment TGO_CTA_PAIR=1; falls back to 1 on a device that cannot co-schedule a pair).
+static int wanted_cta_group() {
+    static const int v = [] {
+        const char* e = getenv("TGO_CTA_PAIR");
+        return (e != nullptr && e[0] == '1') ? 2 : 1;
+    }();
+    return v;
 }
 
 struct Problem {
@@ -410,7 +432,14 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
     a.nsets = p.nsets;
     a.num_experts = static_cast<int>(p.E);
 
-    const int64_t mtiles = p.mode == kFwd ? ((p.N + kTileM - 1) / kTileM) * p.nsets : p.K / kTileM;
+    int cg = wanted_cta_group();
+    int pairs = 0;
+    if (cg == 2) {
+        pairs = max_pairs(p.qt, p.mode);
+        if (pairs < 1) cg = 1;
+    }
+    const int64_t tile_m = static_cast<int64_t>(kTileM) * cg;
+    const int64_t mtiles = p.mode == kFwd ? ((p.N + tile_m - 1) / tile_m) * p.nsets : p.K / tile_m;
     int64_t max_tasks;
     if (p.experts == nullptr) {
         a.dense_tasks = static_cast<int>((p.rows + kTileTok - 1) / kTileTok);
@@ -424,10 +453,14 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
         a.tasks = reinterpret_cast<const int4*>(static_cast<const uint8_t*>(p.ws) + 16);
         max_tasks = cap;
     }
-    int64_t grid = max_tasks * mtiles;
-    if (grid > num_sms()) grid = num_sms();
+    int64_t grid = max_tasks * mtiles;  // persistent CTAs (pairs) never outnumber the tiles
+    const int64_t limit = cg == 2 ? pairs : num_sms();
+    if (grid > limit) grid = limit;
     if (grid < 1) grid = 1;
-    return dispatch_gemm(p.qt, p.mode, a, static_cast<int>(grid), stream);
+    if (getenv("TGO_DEBUG_LAUNCH") != nullptr)
+        fprintf(stderr, "tgo launch: mode %d cta_group %d pairs %d grid %lld tiles<=%lld\n", p.mode, cg, pairs,
+                (long long)(grid * cg), (long long)(max_tasks * mtiles));
+    return dispatch_gemm(p.qt, p.mode, cg, a, static_cast<int>(grid * cg), stream);
 }
 
 // ------------------------------------------------------------------ built-in tile-list scratch
