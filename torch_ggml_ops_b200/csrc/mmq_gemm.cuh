@@ -53,10 +53,19 @@ constexpr int kWgtTileBytes = kTileM * 128;
 #define TGO_WGT_STAGES_MAX 3
 #endif
 #ifndef TGO_PAIR_ACT_STAGES
-#define TGO_PAIR_ACT_STAGES 6
+#define TGO_PAIR_ACT_STAGES 3
 #endif
 #ifndef TGO_PAIR_WGT_STAGES_MAX
-#define TGO_PAIR_WGT_STAGES_MAX 4
+#define TGO_PAIR_WGT_STAGES_MAX 2
+#endif
+// 64-element steps per pipeline stage ("super-step").  The UMMA issuer pays one barrier wait and
+// one commit per stage whatever its size, and every tcgen05 instruction costs that thread some
+// 50-70 cycles, so with short UMMAs (few tokens) a stage of one step makes the issuer the limit.
+#ifndef TGO_SUBSTEPS
+#define TGO_SUBSTEPS 1
+#endif
+#ifndef TGO_PAIR_SUBSTEPS
+#define TGO_PAIR_SUBSTEPS 2
 #endif
 #ifndef TGO_PAIR_RAW_STAGES_FWD
 #define TGO_PAIR_RAW_STAGES_FWD 3
@@ -68,11 +77,16 @@ constexpr int kDecodeWarps = 8;        // warps of one decode group (256 threads
 constexpr int kDecodeGroups = 2;       // groups take alternate steps, so two steps decode at once
 constexpr int kFirstDecodeWarp = 4;
 constexpr int kFirstEpilogueWarp = kFirstDecodeWarp + kDecodeWarps * kDecodeGroups;  // multiple of 4
-constexpr int kGemmThreads = (kFirstEpilogueWarp + 4) * 32;
+#ifndef TGO_EPILOGUE_WARPS
+#define TGO_EPILOGUE_WARPS 4
+#endif
+constexpr int kEpilogueWarps = TGO_EPILOGUE_WARPS;   // 4 or 8: one or two per TMEM lane quarter (two take alternate 16-token chunks)
+static_assert(kEpilogueWarps == 4 || kEpilogueWarps == 8, "epilogue warps");
+constexpr int kGemmThreads = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
 constexpr int kTmemCols = 512;       // two accumulators of 256 columns
 constexpr int kNumBoxes = 5;         // activation TMA boxes of 256, 128, 64, 32, 16 rows
 constexpr int kSmemLimit = 232448;   // 227 KB opt-in limit per CTA
-constexpr int kEpiStageBytes = 4 * 32 * 64;  // per epilogue warp: 32 tokens x 32 outputs, bf16
+constexpr int kEpiStageBytes = kEpilogueWarps * 16 * 64;  // per epilogue warp: 16 tokens x 32 outputs, bf16
 
 struct ActMaps {
     CUtensorMap box[kNumBoxes];
@@ -119,8 +133,12 @@ struct GemmArgs {
 template <int QT, int MODE, int CG>
 struct GemmCfg {
     using Fmt = BlockFmt<QT>;
+    static constexpr int kSub = CG == 2 ? TGO_PAIR_SUBSTEPS : TGO_SUBSTEPS;   // steps per stage
+    static_assert(kSub == 1 || kSub == kDecodeGroups, "a stage holds one step, or one step per decode group");
     static constexpr int kActRows = kTileTok / CG;              // token rows staged by one CTA
-    static constexpr int kActTileBytes = kActRows * 128;
+    static constexpr int kActTileBytes = kActRows * 128;        // one step of activations
+    static constexpr int kActStageBytes = kSub * kActTileBytes;
+    static constexpr int kWgtStageBytes = kSub * kWgtTileBytes;
     static constexpr int kActStages = CG == 2 ? TGO_PAIR_ACT_STAGES : TGO_ACT_STAGES;
     static constexpr int kWgtStagesMax = CG == 2 ? TGO_PAIR_WGT_STAGES_MAX : TGO_WGT_STAGES_MAX;
     static constexpr int kTokPad = CG == 2 ? 32 : 16;           // token padding of a tile (UMMA N granularity)
@@ -134,12 +152,12 @@ struct GemmCfg {
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kGridBytes = QT == QT_IQ2_S ? 8192 : 0;
     static constexpr int kFixed = 1024 /*alignment slack*/ + 512 /*barriers etc.*/ + 128 /*read slack*/ + kEpiStageBytes +
-                                  kActStages * kActTileBytes + kRawBytes + kGridBytes;
-    static constexpr int kWgtStagesFit = (kSmemLimit - kFixed) / kWgtTileBytes;
+                                  kActStages * kActStageBytes + kRawBytes + kGridBytes;
+    static constexpr int kWgtStagesFit = (kSmemLimit - kFixed) / kWgtStageBytes;
     static constexpr int kWgtStagesCap = kWgtStagesMax < kActStages ? kWgtStagesMax : kActStages;
     static constexpr int kWgtStages = kWgtStagesFit >= kWgtStagesCap ? kWgtStagesCap : kWgtStagesFit;
     static_assert(kWgtStages >= 2, "shared memory budget");
-    static constexpr int kSmemBytes = kFixed + kWgtStages * kWgtTileBytes;
+    static constexpr int kSmemBytes = kFixed + kWgtStages * kWgtStageBytes;
 };
 
 struct TileInfo {
@@ -198,7 +216,8 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     using Cfg = GemmCfg<QT, MODE, CG>;
     using Fmt = BlockFmt<QT>;
     constexpr int NA = Cfg::kWgtStages, NB = Cfg::kActStages, NR = Cfg::kRawStages;
-    constexpr int kActTileBytes = Cfg::kActTileBytes;
+    constexpr int kActTileBytes = Cfg::kActTileBytes, kActStageBytes = Cfg::kActStageBytes;
+    constexpr int kWgtStageBytes = Cfg::kWgtStageBytes, KS = Cfg::kSub;
     // CTA pair: rank 0 (the leader) owns the barriers both CTAs feed (full, acc_empty) and issues
     // the UMMAs; every CTA owns the barriers only it waits on (done, raw, acc_full).
     const int rank = CG == 2 ? static_cast<int>(cluster_ctarank()) : 0;
@@ -212,8 +231,8 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
 
     // carve-up (all operand tiles 1024-byte aligned)
     const uint32_t act_s = smem_base;
-    const uint32_t wgt_s = act_s + NB * kActTileBytes;
-    const uint32_t raw_s = wgt_s + NA * kWgtTileBytes;
+    const uint32_t wgt_s = act_s + NB * kActStageBytes;
+    const uint32_t raw_s = wgt_s + NA * kWgtStageBytes;
     const uint32_t grid_s = raw_s + Cfg::kRawBytes + 128;
     const uint32_t epi_s = grid_s + Cfg::kGridBytes;
     const uint32_t misc_s = epi_s + kEpiStageBytes;
@@ -242,7 +261,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     const int mtiles_set = MODE == kFwd ? (N + CG * kTileM - 1) / (CG * kTileM) : K / (CG * kTileM);
     const int mtiles = MODE == kFwd ? mtiles_set * args.nsets : mtiles_set;
     const int steps_set = MODE == kFwd ? K / kStepK : (N + kStepK - 1) / kStepK;
-    const int nsteps = MODE == kFwd ? steps_set : steps_set * args.nsets;
+    const int nsteps = MODE == kFwd ? steps_set : steps_set * args.nsets;   // 64-element steps of a tile
+    const int nstages = (nsteps + KS - 1) / KS;                              // pipeline stages of a tile
+    const int nsteps_pad = nstages * KS;   // a stage's missing steps are fed zeros
     const int ntasks = args.tasks != nullptr ? *args.task_count : args.dense_tasks;
     const long long total_tiles = static_cast<long long>(ntasks) * mtiles;
 
@@ -250,14 +271,14 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         // full: the leader's activation producer (with the byte count of both halves) - or both
         // producers when they copy with plain loads - and the decode warps of every CTA
         for (int i = 0; i < NB; ++i) {
-            mbar_init(bar_full + 8 * i, (args.use_tma ? 1 : CG) + CG * kDecodeWarps);
+            mbar_init(bar_full + 8 * i, (args.use_tma ? 1 : CG) + CG * kDecodeWarps * KS);
             mbar_init(bar_done + 8 * i, 1);
         }
         for (int i = 0; i < NR; ++i) {
             mbar_init(bar_raw_full + 8 * i, 1);
             mbar_init(bar_raw_empty + 8 * i, MODE == kFwd ? kDecodeWarps * kDecodeGroups : kDecodeWarps);
         }
-        for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, 4 * CG); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, kEpilogueWarps * CG); }
         *abort_word = 0;
         mbar_fence_init();
     }
@@ -293,28 +314,34 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                     TileInfo t;
                     if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
-                    for (int step = 0; step < nsteps; ++step, ++it) {
+                    for (int stage = 0; stage < nstages; ++stage, ++it) {
                         const uint32_t s = it % NB, ph = (it / NB) & 1u;
                         if (!mbar_wait(bar_done + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty)) { ok = false; break; }
-                        const int set = MODE == kFwd ? 0 : step / steps_set;
-                        const int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
-                        // the leader announces the bytes of the whole tile; each CTA copies its share
+                        // the leader announces the bytes of the whole stage; each CTA copies its share
                         // of the token rows (all of them, or its half) and the bytes count on the
                         // leader's barrier
                         const uint32_t bar = lead_full + 8 * s;
-                        if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, static_cast<uint32_t>(t.ntok_pad) * 128u);
-                        uint32_t dst = act_s + s * kActTileBytes;
-                        int rem = t.ntok_pad / CG;
-                        int row = t.row0 + rank * rem;
+                        if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, static_cast<uint32_t>(t.ntok_pad) * 128u * KS);
 #pragma unroll
-                        for (int b = 0; b < kNumBoxes; ++b) {
-                            const int h = 256 >> b;
-                            if (h <= Cfg::kActRows && rem >= h) {
-                                if (CG == 2) tma_load_2d_pair(dst, &args.act_maps[set].box[b], bar, red0, row);
-                                else tma_load_2d(dst, &args.act_maps[set].box[b], bar, red0, row);
-                                dst += h * 128;
-                                row += h;
-                                rem -= h;
+                        for (int ks = 0; ks < KS; ++ks) {
+                            const int step = stage * KS + ks;
+                            int set = MODE == kFwd ? 0 : step / steps_set;
+                            // a step past the end reads columns outside the matrix: TMA fills zeros
+                            int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
+                            if (step >= nsteps) { set = 0; red0 = (steps_set + (step - nsteps)) * kStepK; }
+                            uint32_t dst = act_s + s * kActStageBytes + ks * kActTileBytes;
+                            int rem = t.ntok_pad / CG;
+                            int row = t.row0 + rank * rem;
+#pragma unroll
+                            for (int b = 0; b < kNumBoxes; ++b) {
+                                const int h = 256 >> b;
+                                if (h <= Cfg::kActRows && rem >= h) {
+                                    if (CG == 2) tma_load_2d_pair(dst, &args.act_maps[set].box[b], bar, red0, row);
+                                    else tma_load_2d(dst, &args.act_maps[set].box[b], bar, red0, row);
+                                    dst += h * 128;
+                                    row += h;
+                                    rem -= h;
+                                }
                             }
                         }
                     }
@@ -329,26 +356,30 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
                 if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
-                for (int step = 0; step < nsteps; ++step, ++it) {
+                for (int stage = 0; stage < nstages; ++stage, ++it) {
                     const uint32_t s = it % NB, ph = (it / NB) & 1u;
                     if (!lane0_wait(bar_done + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty, lane)) { ok = false; break; }
-                    const int set = MODE == kFwd ? 0 : step / steps_set;
-                    const int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
-                    const __nv_bfloat16* src = args.act[set];
-                    uint8_t* dst = act_g + s * kActTileBytes;
-                    const int my_rows = t.ntok_pad / CG;
-                    for (int idx = lane; idx < my_rows * 8; idx += 32) {
-                        const int r = idx >> 3, c = idx & 7;
-                        const long long grow = static_cast<long long>(t.row0) + rank * my_rows + r;
-                        alignas(16) __nv_bfloat16 v[8];
+                    for (int ks = 0; ks < KS; ++ks) {
+                        const int step = stage * KS + ks;
+                        int set = MODE == kFwd ? 0 : step / steps_set;
+                        int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
+                        if (step >= nsteps) { set = 0; red0 = red_total; }   // a step past the end: zeros
+                        const __nv_bfloat16* src = args.act[set];
+                        uint8_t* dst = act_g + s * kActStageBytes + ks * kActTileBytes;
+                        const int my_rows = t.ntok_pad / CG;
+                        for (int idx = lane; idx < my_rows * 8; idx += 32) {
+                            const int r = idx >> 3, c = idx & 7;
+                            const long long grow = static_cast<long long>(t.row0) + rank * my_rows + r;
+                            alignas(16) __nv_bfloat16 v[8];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const int col = red0 + c * 8 + e;
-                            v[e] = (grow < args.rows && col < red_total) ? src[grow * red_total + col]
-                                                                         : __float2bfloat16(0.0f);
+                            for (int e = 0; e < 8; ++e) {
+                                const int col = red0 + c * 8 + e;
+                                v[e] = (grow < args.rows && col < red_total) ? src[grow * red_total + col]
+                                                                             : __float2bfloat16(0.0f);
+                            }
+                            *reinterpret_cast<uint4*>(dst + r * 128 + ((c ^ (r & 7)) << 4)) =
+                                *reinterpret_cast<const uint4*>(v);
                         }
-                        *reinterpret_cast<uint4*>(dst + r * 128 + ((c ^ (r & 7)) << 4)) =
-                            *reinterpret_cast<const uint4*>(v);
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
@@ -360,10 +391,10 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ UMMA issuer (one thread)
-        // This thread's instruction stream is the serial spine of the kernel: every step it waits,
-        // issues four UMMAs and one commit, each a dependent chain of its own.  The loop therefore
-        // keeps stage counters, barrier addresses and the low descriptor words as running values
-        // (one add per use) and builds nothing from scratch inside a step.
+        // This thread's instruction stream is the serial spine of the kernel: per stage it waits
+        // once, issues 4 * KS UMMAs and commits once (twice for a pair); every one of these costs
+        // it 50-70 cycles whatever the UMMA's size.  The loop keeps stage counters, barrier
+        // addresses and the low descriptor words as running values (one add per use).
         if (lane == 0 && rank == 0) {
             constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version, SWIZZLE_128B
             constexpr uint32_t kLboA = MODE == kFwd ? 16u : 8192u;                 // forward K-major, backward MN-major
@@ -378,10 +409,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             uint32_t a_lo = a_lo0, b_lo = b_lo0, sa = 0, sb = 0, ph = 0;
             uint32_t full_bar = bar_full, done_bar = bar_done;
             uint32_t tl = 0;
-            bool ok = true;
-            // the test of the next step's barrier is issued before this step's UMMAs, so its latency
-            // overlaps their issue; a negative answer only means "ask again, blocking"
-            bool ready = false;
+            bool ok = true, ready = false;
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
                 if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
@@ -392,29 +420,33 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 const uint32_t d_tmem = tmem_base + acc * kTileTok;
                 const uint32_t idesc =
                     umma_idesc_bf16(static_cast<uint32_t>(t.ntok_pad), MODE == kBwd ? 1u : 0u, 0u, 128u * CG);
-                for (int step = 0; step < nsteps; ++step) {
+                for (int stage = 0; stage < nstages; ++stage) {
                     if (!ready && !mbar_wait(full_bar, ph, abort_word, kAbortWgtFull)) { ok = false; break; }
                     const uint32_t cur_done = done_bar, cur_a = a_lo, cur_b = b_lo;
                     // advance the rings (independent of the UMMAs below, so it overlaps their issue)
-                    a_lo += kWgtTileBytes >> 4;
+                    a_lo += kWgtStageBytes >> 4;
                     if (++sa == NA) { sa = 0; a_lo = a_lo0; }
-                    b_lo += kActTileBytes >> 4;
+                    b_lo += kActStageBytes >> 4;
                     full_bar += 8;
                     done_bar += 8;
                     if (++sb == NB) { sb = 0; b_lo = b_lo0; full_bar = bar_full; done_bar = bar_done; ph ^= 1u; }
-                    ready = mbar_try_wait(full_bar, ph);
-                    if (CG == 2) {
-                        umma_bf16_lohi_pair(d_tmem, cur_a, cur_b, kDescHi, idesc, step != 0 ? 1u : 0u);
+                    // with short stages, test the next stage's barrier now: the answer arrives while
+                    // the UMMAs issue; "no" only means "ask again, blocking"
+                    ready = KS == 1 ? mbar_try_wait(full_bar, ph) : false;
 #pragma unroll
-                        for (uint32_t kk = 1; kk < kStepK / 16; ++kk)
-                            umma_bf16_lohi_pair(d_tmem, cur_a + kk * kStepA, cur_b + kk * kStepB, kDescHi, idesc, 1u);
+                    for (uint32_t ks = 0; ks < static_cast<uint32_t>(KS); ++ks) {
+                        const uint32_t sa_lo = cur_a + ks * (kWgtTileBytes >> 4), sb_lo = cur_b + ks * (kActTileBytes >> 4);
+#pragma unroll
+                        for (uint32_t kk = 0; kk < kStepK / 16; ++kk) {
+                            const uint32_t accum = (ks | kk) != 0 ? 1u : (stage != 0 ? 1u : 0u);
+                            if (CG == 2) umma_bf16_lohi_pair(d_tmem, sa_lo + kk * kStepA, sb_lo + kk * kStepB, kDescHi, idesc, accum);
+                            else umma_bf16_lohi(d_tmem, sa_lo + kk * kStepA, sb_lo + kk * kStepB, kDescHi, idesc, accum);
+                        }
+                    }
+                    if (CG == 2) {
                         umma_commit_pair(cur_done);
                         umma_commit_pair(peer_done + (cur_done - bar_done));
                     } else {
-                        umma_bf16_lohi(d_tmem, cur_a, cur_b, kDescHi, idesc, step != 0 ? 1u : 0u);
-#pragma unroll
-                        for (uint32_t kk = 1; kk < kStepK / 16; ++kk)
-                            umma_bf16_lohi(d_tmem, cur_a + kk * kStepA, cur_b + kk * kStepB, kDescHi, idesc, 1u);
                         umma_commit(cur_done);
                     }
                 }
@@ -441,7 +473,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
                 if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
-                const int nraw = MODE == kFwd ? nkb : nsteps;
+                const int nraw = MODE == kFwd ? nkb : nsteps_pad;
                 for (int ri = 0; ri < nraw; ++ri, ++itr) {
                     const uint32_t r = itr % NR, ph = (itr / NR) & 1u;
                     if (!mbar_wait(bar_raw_empty + 8 * r, ph ^ 1u, abort_word, kAbortRawEmpty)) { ok = false; break; }
@@ -450,6 +482,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                         set = t.set; n_first = t.m0; kb = ri;
                     } else {
                         set = ri / steps_set; n_first = (ri - set * steps_set) * kStepK; kb = t.m0 >> 8;
+                        if (ri >= nsteps) { set = 0; n_first = 0; }   // a step past the end: decoded as zeros
                     }
                     const long long g0 = static_cast<long long>(t.expert) * N + n_first;  // first global weight row
                     const uint32_t bar = bar_raw_full + 8 * r;
@@ -472,17 +505,8 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         // stage (a super-block column of 128 rows) serves four steps, two per group; a thread
         // keeps its row and 32-weight half for the whole tile.  Backward: one raw stage (64 rows)
         // per step; a thread keeps its row slot and 32-weight group.
-        // A group owns two of the SM's four warp schedulers (a warp's scheduler is its index
-        // mod 4): the warps of one scheduler are then always in the same phase, so a group that
-        // waits is never starved of issue slots by the other group's arithmetic.
-#ifdef TGO_GROUPS_INTERLEAVED
         const int group = (warp - kFirstDecodeWarp) / kDecodeWarps;
         const int dt = threadIdx.x - (kFirstDecodeWarp + group * kDecodeWarps) * 32;  // 0..255
-#else
-        const int dw = warp - kFirstDecodeWarp;             // 0..15; kFirstDecodeWarp is a multiple of 4
-        const int group = (dw & 3) >> 1;
-        const int dt = (((dw >> 2) << 1) | (dw & 1)) * 32 + lane;  // 0..255 inside the group
-#endif
         const int row = MODE == kFwd ? dt >> 1 : dt >> 2;     // weight row inside the raw stage
         const int sub = MODE == kFwd ? dt & 1 : dt & 3;       // which 32 weights of the step's span
         // byte offsets of this thread's four 16-byte chunks inside a decoded tile (128B swizzle)
@@ -500,8 +524,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
 
         // waits until decoded-weight stage (it % NA) is free, decodes into it and signals the step
         auto emit = [&](uint32_t blk, int g, bool valid, uint32_t raw_bar_to_release) -> bool {
-            if (it >= static_cast<uint32_t>(NA)) {
-                const uint32_t j = it - NA;  // the step that last used this stage
+            const uint32_t stg = it / KS, ks = it % KS;   // pipeline stage (running index) and step inside it
+            if (stg >= static_cast<uint32_t>(NA)) {
+                const uint32_t j = stg - NA;  // the stage that last used this slot
                 if (!all_wait(bar_done + 8 * (j % NB), (j / NB) & 1u, abort_word, kAbortWgtEmpty)) return false;
             }
             uint4 o[4];
@@ -510,13 +535,13 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             } else {
                 o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
             }
-            const uint32_t tile_s = wgt_s + (it % NA) * kWgtTileBytes;
+            const uint32_t tile_s = wgt_s + (stg % NA) * kWgtStageBytes + ks * kWgtTileBytes;
 #pragma unroll
             for (int c = 0; c < 4; ++c) sts128(tile_s + coff[c], o[c]);
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                if (CG == 2) mbar_arrive_cluster(lead_full + 8 * (it % NB)); else mbar_arrive(bar_full + 8 * (it % NB));
+                if (CG == 2) mbar_arrive_cluster(lead_full + 8 * (stg % NB)); else mbar_arrive(bar_full + 8 * (stg % NB));
                 if (raw_bar_to_release != 0) mbar_arrive(raw_bar_to_release);
             }
             it += kDecodeGroups;
@@ -549,13 +574,13 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 const int g = ((t.m0 >> 7) & 1) * 4 + sub;
                 const int kb = t.m0 >> 8;
                 // this group's first step of the tile: running index parity must equal the group
-                for (int step = static_cast<int>((it - raw_it) & 0x7FFFFFFFu); step < nsteps; step += kDecodeGroups) {
+                for (int step = static_cast<int>((it - raw_it) & 0x7FFFFFFFu); step < nsteps_pad; step += kDecodeGroups) {
                     const uint32_t ri = raw_it + step;
                     const uint32_t r = ri % NR, rph = (ri / NR) & 1u;
                     if (!all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull)) { ok = false; break; }
                     const int set = step >= steps_set ? 1 : 0;
                     const int n_first = (step - set * steps_set) * kStepK;
-                    const bool valid = n_first + row < N;
+                    const bool valid = step < nsteps && n_first + row < N;
                     uint32_t blk = 0;
                     if (valid) {
                         int slot = row, mis = 0;
@@ -568,12 +593,13 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     }
                     if (!emit(blk, g, valid, bar_raw_empty + 8 * r)) { ok = false; break; }
                 }
-                raw_it += nsteps;
+                raw_it += nsteps_pad;
             }
         }
     } else if (warp >= kFirstEpilogueWarp) {
         // ------------------------------------------------------------ epilogue
-        const int quad = warp & 3;
+        const int quad = warp & 3;                              // TMEM lanes 32 * quad .. + 31
+        const int ehalf = (warp - kFirstEpilogueWarp) >> 2;     // which of the alternate 16-token chunks
         uint32_t tl = 0;
         const int mdim = MODE == kFwd ? N : K;
         for (long long tile = cta; tile < total_tiles; tile += ncta) {
@@ -587,27 +613,20 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             const int mq = t.m0 + quad * 32;  // first output column of this warp
             __nv_bfloat16* out_base = args.out[MODE == kFwd ? t.set : 0] + static_cast<long long>(t.row0) * mdim;
             if ((mdim & 7) == 0 && mq + 32 <= mdim) {
-                // Transposing path: the warp's 32 outputs x 32 tokens go through a private staging
+                // Transposing path: the warp's 32 outputs x 16 tokens go through a private staging
                 // tile [token][32 outputs] so that global stores are 16 bytes per lane.
-                uint8_t* stage = epi_g + quad * (32 * 64);
-                for (int c0 = 0; c0 < t.ntok_pad; c0 += 32) {
-                    uint32_t v[32];
-                    if (c0 + 32 <= t.ntok_pad) {
-                        tmem_ld32(taddr + c0, v);
-                    } else {  // last 16 padded columns of the tile
-                        uint32_t h[16];
-                        tmem_ld16(taddr + c0, h);
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) { v[j] = h[j]; v[16 + j] = 0u; }
-                    }
+                uint8_t* stage = epi_g + (warp - kFirstEpilogueWarp) * (16 * 64);
+                for (int c0 = 16 * ehalf; c0 < t.ntok_pad; c0 += 4 * kEpilogueWarps) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + c0, v);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
+                    for (int j = 0; j < 16; ++j)
                         *reinterpret_cast<__nv_bfloat16*>(stage + j * 64 + lane * 2) =
                             __float2bfloat16(__uint_as_float(v[j]));
                     __syncwarp();
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
+                    for (int i = 0; i < 2; ++i) {
                         const int r = (lane >> 2) + 8 * i, part = lane & 3;
                         const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 64 + part * 16);
                         if (c0 + r < t.ntok)
@@ -619,7 +638,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 const int m = mq + lane;
                 const bool m_ok = m < mdim;
                 __nv_bfloat16* out = out_base + m;
-                for (int c0 = 0; c0 < t.ntok_pad; c0 += 16) {
+                for (int c0 = 16 * ehalf; c0 < t.ntok_pad; c0 += 4 * kEpilogueWarps) {
                     uint32_t v[16];
                     tmem_ld16(taddr + c0, v);
                     tmem_ld_wait();

@@ -340,12 +340,12 @@ static int max_pairs(int qt, int mode) {
     }
 }
 
-// 1: tiles of 128 weight rows on single CTAs (the default); 2: tiles of 256 rows on CTA pairs
-// (environment TGO_CTA_PAIR=1; falls back to 1 on a device that cannot co-schedule a pair).
+// 2: tiles of 256 weight rows on CTA pairs (the default); 1: tiles of 128 rows on single CTAs
+// (environment TGO_CTA_PAIR=0, or a device that cannot co-schedule a pair).
 static int wanted_cta_group() {
     static const int v = [] {
         const char* e = getenv("TGO_CTA_PAIR");
-        return (e != nullptr && e[0] == '1') ? 2 : 1;
+        return (e != nullptr && e[0] == '0') ? 1 : 2;
     }();
     return v;
 }
