@@ -508,6 +508,74 @@ def reference_arm(args):
     print(json.dumps(line))
 
 
+def sweep_arm(args):
+    """Kernel-level TFLOP/s of the other benchmark configurations (dense config 1 and 2 for all
+    five quant types, grouped config 3, pair + down projection of config 4), device-resident,
+    CUDA events, one JSON line per case.  Not the contract line: a table for the design notes."""
+    from torch_ggml_ops_b200 import native
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        tot = 0.0
+        for _ in range(n):
+            flush.zero_()   # evict the operands from L2 between repeats
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            tot += a.elapsed_time(b)
+        return tot / n
+
+    def report(name, flops, f_ms, b_ms):
+        print(json.dumps({"case": name, "fwd_ms": round(f_ms, 4), "fwd_tflops": round(flops / f_ms / 1e9, 1),
+                          "dx_ms": round(b_ms, 4), "dx_tflops": round(flops / b_ms / 1e9, 1)}), flush=True)
+
+    def bf16(rows, cols, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        return torch.randn(rows, cols, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+
+    names = {11: "Q3_K", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 22: "IQ2_S"}
+    dense = [(12, 512, 2048, 2048)] + [(qt, 4096, n, k) for qt in (22, 11, 12, 13, 14) for (n, k) in ((4096, 2048), (2048, 4096))]
+    for qt, M, N, K in dense:
+        w = torch.from_numpy(synthetic_expert_weights(qt, 1, N, K, 11)).to(dev)[0]
+        x, dy = bf16(M, K, 1), bf16(M, N, 2)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        dx = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+        f = timed(lambda: native.mmq_fwd(x, w, y, M, N, K, qt), args.steps)
+        b = timed(lambda: native.mmq_dx(dy, w, dx, M, N, K, qt), args.steps)
+        report(f"dense {names[qt]} M={M} N={N} K={K}", 2.0 * M * N * K, f, b)
+
+    def grouped(qt, E, N, K, tokens, top_k, pair, label):
+        ids = synthetic_routing(tokens, E, top_k, 2.0, 2024)
+        counts = np.bincount(ids.reshape(-1), minlength=E)
+        eo = torch.tensor(np.cumsum(counts), dtype=torch.int32, device=dev)
+        ei = torch.arange(E, dtype=torch.int64, device=dev)
+        R = tokens * top_k
+        w0 = torch.from_numpy(synthetic_expert_weights(qt, E, N, K, 21)).to(dev)
+        w1 = torch.from_numpy(synthetic_expert_weights(qt, E, N, K, 22)).to(dev) if pair else None
+        x, dy0 = bf16(R, K, 3), bf16(R, N, 4)
+        dy1 = bf16(R, N, 5) if pair else None
+        y0 = torch.empty(R, N, dtype=torch.bfloat16, device=dev)
+        y1 = torch.empty(R, N, dtype=torch.bfloat16, device=dev) if pair else None
+        dx = torch.empty(R, K, dtype=torch.bfloat16, device=dev)
+        ws = torch.empty(native.grouped_workspace_bytes(R, E), dtype=torch.uint8, device=dev)
+        f = timed(lambda: native.grouped_fwd(x, w0, w1, y0, y1, ei, eo, E, R, N, K, qt, ws), args.steps)
+        b = timed(lambda: native.grouped_dx(dy0, dy1, w0, w1, dx, ei, eo, E, R, N, K, qt, ws), args.steps)
+        report(label, 2.0 * R * N * K * (2 if pair else 1), f, b)
+
+    grouped(12, 256, 512, 2048, 8192, 8, False, "config 3: grouped Q4_K 256 x (512 x 2048), 65536 routed rows")
+    grouped(13, 256, 512, 2048, 16384, 8, True, "config 4: gate/up pair Q5_K 256 x (512 x 2048), 131072 routed rows")
+    grouped(14, 256, 2048, 512, 16384, 8, False, "config 4: down Q6_K 256 x (2048 x 512), 131072 routed rows")
+    grouped(22, 256, 512, 2048, 16384, 8, True, "config 5 shapes on one GPU: gate/up pair IQ2_S, 131072 routed rows")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -521,8 +589,12 @@ def main():
                     help="multi-GPU row exchange: this library's peer-memory kernels, or NCCL all-to-all")
     ap.add_argument("--profile", action="store_true",
                     help="single GPU only: run warm-up + steps of the device-resident step and exit (for ncu)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="single GPU only: kernel-level TFLOP/s of the other benchmark configurations, one JSON line each")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.sweep:
+        sweep_arm(args)
+    elif args.impl == "reference":
         reference_arm(args)
     else:
         gpu_arm(args)

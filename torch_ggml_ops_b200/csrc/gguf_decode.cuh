@@ -20,14 +20,17 @@ namespace tgo {
 enum : int { QT_Q3_K = 11, QT_Q4_K = 12, QT_Q5_K = 13, QT_Q6_K = 14, QT_IQ2_S = 22 };
 
 template <int QT> struct BlockFmt;
-// kBytes: block size.  kAligned: every block starts 16-byte aligned.  kCopy: bytes copied per
-// block window (covers the block from the aligned address below its start).  kSlot: distance
-// between windows in shared memory (kCopy plus slack for the trailing funnel-shift word).
-template <> struct BlockFmt<QT_Q4_K> { static constexpr int kBytes = 144, kAligned = 1, kCopy = 144, kSlot = 144; };
-template <> struct BlockFmt<QT_Q5_K> { static constexpr int kBytes = 176, kAligned = 1, kCopy = 176, kSlot = 176; };
-template <> struct BlockFmt<QT_Q6_K> { static constexpr int kBytes = 210, kAligned = 0, kCopy = 224, kSlot = 240; };
-template <> struct BlockFmt<QT_Q3_K> { static constexpr int kBytes = 110, kAligned = 0, kCopy = 128, kSlot = 144; };
-template <> struct BlockFmt<QT_IQ2_S> { static constexpr int kBytes = 82, kAligned = 0, kCopy = 96, kSlot = 112; };
+// kBytes: block size.  kAligned: every block starts 16-byte aligned.  kCopy: bytes that cover the
+// block from the aligned address below its start.  kSlot: distance between block windows in shared
+// memory: kCopy plus slack for the trailing funnel-shift word, and chosen so that the windows of
+// consecutive rows start in different banks (a pitch of 128 bytes would put every row of a warp on
+// the same bank).  kBox: bytes per window that the GEMM's TMA box loads copy (= kSlot: the box rows
+// land back to back in shared memory, so the box width is the pitch).
+template <> struct BlockFmt<QT_Q4_K> { static constexpr int kBytes = 144, kAligned = 1, kCopy = 144, kSlot = 144, kBox = 144; };
+template <> struct BlockFmt<QT_Q5_K> { static constexpr int kBytes = 176, kAligned = 1, kCopy = 176, kSlot = 176, kBox = 176; };
+template <> struct BlockFmt<QT_Q6_K> { static constexpr int kBytes = 210, kAligned = 0, kCopy = 224, kSlot = 240, kBox = 240; };
+template <> struct BlockFmt<QT_Q3_K> { static constexpr int kBytes = 110, kAligned = 0, kCopy = 128, kSlot = 144, kBox = 144; };
+template <> struct BlockFmt<QT_IQ2_S> { static constexpr int kBytes = 82, kAligned = 0, kCopy = 96, kSlot = 112, kBox = 112; };
 
 __host__ __device__ constexpr int block_bytes_of(int qt) {
     return qt == QT_Q3_K ? 110 : qt == QT_Q4_K ? 144 : qt == QT_Q5_K ? 176 : qt == QT_Q6_K ? 210

@@ -6,26 +6,33 @@
 //   backward (kBwd):  dX[t, k] = sum_n dY[t, n] * W[n, k]      (reference: csrc/ck/mmq_backward.cuh:496-1004,
 //                                                                csrc/ck/grouped_mmq_backward.cuh:42-152, 308-458)
 //
-// The weight side sits on the UMMA M axis (128 TMEM lanes = 128 out-features forward, 128
+// The weight side sits on the UMMA M axis (128 TMEM lanes per CTA = 128 out-features forward, 128
 // in-features backward) and the tokens on the UMMA N axis (16..256 TMEM columns), so a ragged
-// expert group costs at most 15 padded token columns and one decoded weight tile is reused by up
-// to 256 tokens.  Raw GGUF super-blocks are staged into shared memory by TMA, decoded there to bf16
-// in the 128-byte-swizzled operand layout by eight decode warps, and consumed by tcgen05.mma
-// (kind::f16, bf16 x bf16 -> fp32 in TMEM).  The same decoded image [weight row n][64 k] is a
-// K-major operand forward and an MN-major operand backward, so neither direction transposes.
-// The reduction order of every output element is fixed (ascending reduction index, 16 per UMMA),
-// independent of tiling, which makes grouped == dense and pair == two singles bit-exact.
+// expert group costs at most 15 (pair: 31) padded token columns and one decoded weight tile is
+// reused by up to 256 tokens.  Raw GGUF super-blocks are staged into shared memory by TMA, decoded
+// there to bf16 in the 128-byte-swizzled operand layout by sixteen decode warps, and consumed by
+// tcgen05.mma (kind::f16, bf16 x bf16 -> fp32 in TMEM).  The same decoded image
+// [weight row n][64 k] is a K-major operand forward and an MN-major operand backward, so neither
+// direction transposes.  The reduction order of every output element is fixed (ascending
+// reduction index, 16 per UMMA), independent of tiling, which makes grouped == dense and
+// pair == two singles bit-exact.
+//
+// CG = 2 (the default): two CTAs of a cluster share a token tile and cover 256 weight rows with
+// cta_group::2 UMMAs; each CTA decodes its own 128 rows and stages half of the tokens, the
+// leader CTA (cluster rank 0) issues the UMMAs and owns the barriers both CTAs feed.
 //
 // Warp roles (768 threads): 0 activation producer (TMA), 1 UMMA issuer + TMEM owner, 2 raw
-// weight producer (TMA), 3 idle, 4-19 decode (two groups of 8 warps on alternate steps), 20-23
-// epilogue (TMEM -> bf16 -> global).
+// weight producer (TMA), 3 idle, 4-19 decode (two groups of 8 warps on alternate 64-element
+// steps), 20-23 epilogue (TMEM -> bf16 -> global).
 //
-// Synchronisation per 64-element step i (running index over all tiles of the CTA):
-//   full[i % NB]  <- the activation TMA (expect_tx) and the 8 decode warps of the step's group;
-//                    the UMMA issuer waits on it once and issues the step's four UMMAs;
-//   done[i % NB]  <- one tcgen05.commit after those UMMAs; the activation producer waits on it
-//                    before refilling the slot, the decode group of step i + NA waits on it before
-//                    overwriting decoded-weight stage i % NA (NA <= NB);
+// Synchronisation.  A stage is KS steps (1 for a single CTA, 2 for a pair: one step per decode
+// group); stages have running index j over all tiles of the CTA:
+//   full[j % NB]  <- the activation TMA (expect_tx for the whole stage, announced by the leader)
+//                    and the decode warps of the stage's steps (of both CTAs); the UMMA issuer
+//                    waits on it once and issues the stage's 4 * KS UMMAs;
+//   done[j % NB]  <- one tcgen05.commit after those UMMAs (one per CTA of a pair); the activation
+//                    producer waits on it before refilling the slot, the decode warps of stage
+//                    j + NA wait on it before overwriting decoded-weight slot j % NA (NA <= NB);
 //   raw_full / raw_empty: TMA raw-block ring <-> decode;  acc_full / acc_empty: TMEM <-> epilogue.
 // All waits are bounded (ptx.cuh); a wait that gives up unwinds every role to the common exit,
 // which frees TMEM and records a status code.
@@ -144,11 +151,11 @@ struct GemmCfg {
     static constexpr int kTokPad = CG == 2 ? 32 : 16;           // token padding of a tile (UMMA N granularity)
     static constexpr int kRawRows = MODE == kFwd ? 128 : 64;    // block windows per raw stage
     // pair: as many raw stages as fit in about 56 KB (the raw ring has to cover an HBM round trip)
-    static constexpr int kRawFit = 57344 / (kRawRows * Fmt::kCopy);
+    static constexpr int kRawFit = 57344 / (kRawRows * Fmt::kBox);
     static constexpr int kRawMaxPair = MODE == kFwd ? TGO_PAIR_RAW_STAGES_FWD : TGO_PAIR_RAW_STAGES_BWD;
     static constexpr int kRawStages = CG == 2 ? (kRawFit >= kRawMaxPair ? kRawMaxPair : (kRawFit < 2 ? 2 : kRawFit))
                                               : (MODE == kFwd ? 2 : 4);
-    static constexpr int kRawStageBytes = kRawRows * Fmt::kCopy;
+    static constexpr int kRawStageBytes = kRawRows * Fmt::kBox;
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kGridBytes = QT == QT_IQ2_S ? 8192 : 0;
     static constexpr int kFixed = 1024 /*alignment slack*/ + 512 /*barriers etc.*/ + 128 /*read slack*/ + kEpiStageBytes +
@@ -462,7 +469,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------ raw weight producer
-        // One box load per alignment class and stage: rows / P block windows of kCopy bytes each.
+        // One box load per alignment class and stage: rows / P block windows of kBox bytes each.
         if (lane == 0) {
             uint32_t itr = 0;
             bool ok = true;
@@ -486,7 +493,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     }
                     const long long g0 = static_cast<long long>(t.expert) * N + n_first;  // first global weight row
                     const uint32_t bar = bar_raw_full + 8 * r;
-                    mbar_arrive_expect_tx(bar, static_cast<uint32_t>(kRows) * Fmt::kCopy);
+                    mbar_arrive_expect_tx(bar, static_cast<uint32_t>(kRows) * Fmt::kBox);
                     const uint32_t stage_s = raw_s + r * Cfg::kRawStageBytes;
                     for (int c = 0; c < P; ++c) {
                         // first row of class c at or after g0, as a row index inside map c
@@ -494,7 +501,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                         const int y = static_cast<int>((first - c) >> lgP);
                         const int mis_c = (c * args.wgt_row_bytes) & 15;
                         const int x = (mis_c + kb * Fmt::kBytes) & ~15;
-                        tma_load_2d(stage_s + c * (kRows >> lgP) * Fmt::kCopy, &args.wgt_maps[set].cls[c], bar, x, y);
+                        tma_load_2d(stage_s + c * (kRows >> lgP) * Fmt::kBox, &args.wgt_maps[set].cls[c], bar, x, y);
                     }
                 }
             }
@@ -559,7 +566,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     cls = static_cast<int>((gexp + t.m0 + row) & (P - 1));
                     slot = cls * (Cfg::kRawRows >> lgP) + (row >> lgP);
                 }
-                const uint32_t blk0 = raw_s + slot * Fmt::kCopy;
+                const uint32_t blk0 = raw_s + slot * Fmt::kBox;
                 const int mis0 = Fmt::kAligned ? 0 : (cls * args.wgt_row_bytes) & 15;
                 for (int kb = 0; kb < nkb && ok; ++kb, ++raw_it) {
                     const uint32_t r = raw_it % NR, rph = (raw_it / NR) & 1u;
@@ -589,7 +596,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                             slot = cls * (Cfg::kRawRows >> lgP) + (row >> lgP);
                             mis = (((cls * args.wgt_row_bytes) & 15) + kb * Fmt::kBytes) & 15;
                         }
-                        blk = raw_s + r * Cfg::kRawStageBytes + slot * Fmt::kCopy + mis;
+                        blk = raw_s + r * Cfg::kRawStageBytes + slot * Fmt::kBox + mis;
                     }
                     if (!emit(blk, g, valid, bar_raw_empty + 8 * r)) { ok = false; break; }
                 }

@@ -206,11 +206,11 @@ static int make_wgt_maps(WgtMaps& maps, const void* base, int64_t total_rows, in
 
 static int copy_bytes_of(int qt) {
     switch (qt) {
-        case QT_Q3_K: return BlockFmt<QT_Q3_K>::kCopy;
-        case QT_Q4_K: return BlockFmt<QT_Q4_K>::kCopy;
-        case QT_Q5_K: return BlockFmt<QT_Q5_K>::kCopy;
-        case QT_Q6_K: return BlockFmt<QT_Q6_K>::kCopy;
-        default: return BlockFmt<QT_IQ2_S>::kCopy;
+        case QT_Q3_K: return BlockFmt<QT_Q3_K>::kBox;
+        case QT_Q4_K: return BlockFmt<QT_Q4_K>::kBox;
+        case QT_Q5_K: return BlockFmt<QT_Q5_K>::kBox;
+        case QT_Q6_K: return BlockFmt<QT_Q6_K>::kBox;
+        default: return BlockFmt<QT_IQ2_S>::kBox;
     }
 }
 
