@@ -514,8 +514,17 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         // per step; a thread keeps its row slot and 32-weight group.
         const int group = (warp - kFirstDecodeWarp) / kDecodeWarps;
         const int dt = threadIdx.x - (kFirstDecodeWarp + group * kDecodeWarps) * 32;  // 0..255
-        const int row = MODE == kFwd ? dt >> 1 : dt >> 2;     // weight row inside the raw stage
-        const int sub = MODE == kFwd ? dt & 1 : dt & 3;       // which 32 weights of the step's span
+        // Forward: 128 rows x 2 halves, (row, half) = (dt / 2, dt % 2).  Backward: 64 rows x 4
+        // quarters.  For the 16-byte-aligned block types (128-bit loads) (row, quarter) =
+        // (dt % 64, dt / 64): a quarter-warp, which shares one 128-bit store wavefront, then holds
+        // eight different rows of the same quarter, whose swizzled chunks cover all banks; with the
+        // quarter in the low bits two of every four lanes meet on the same banks (the two
+        // 64-column halves of the image are 8 KB apart).  The other types read their blocks as
+        // 32-bit words, many of them common to the four quarters of a row: there (dt / 4, dt % 4)
+        // keeps those loads broadcasts and the eight rows of a warp on different banks.
+        constexpr bool kRowMajorLanes = MODE == kBwd && Fmt::kAligned;
+        const int row = MODE == kFwd ? dt >> 1 : (kRowMajorLanes ? dt & 63 : dt >> 2);   // weight row inside the raw stage
+        const int sub = MODE == kFwd ? dt & 1 : (kRowMajorLanes ? dt >> 6 : dt & 3);     // which 32 weights of the step's span
         // byte offsets of this thread's four 16-byte chunks inside a decoded tile (128B swizzle)
         uint32_t coff[4];
         {
