@@ -370,7 +370,9 @@ def gpu_arm(args):
             # other.  Receive buffers are sized for twice the mean load (the routing is skewed).
             nmb = max(1, args.micro)
             mb_tok = T // nmb
-            peps = [PeerExpertParallel(w_local, qt, E, N, K, capacity_rows=2 * mb_tok * top_k) for _ in range(nmb)]
+            peps = [PeerExpertParallel(w_local, qt, E, N, K, capacity_rows=2 * mb_tok * top_k,
+                                       tokens_per_rank=mb_tok if args.token_level else None, top_k=top_k)
+                    for _ in range(nmb)]
             pep = peps[0]
             mb_streams = [torch.cuda.Stream() for _ in range(nmb)]
             ids32 = ids.to(torch.int32)
@@ -587,6 +589,8 @@ def main():
                     help="multi-GPU peer exchange: micro-batches per step (exchange of one overlaps matmuls of another)")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="multi-GPU row exchange: this library's peer-memory kernels, or NCCL all-to-all")
+    ap.add_argument("--pair-level", dest="token_level", action="store_false",
+                    help="multi-GPU peer exchange: move one row per routed pair instead of one per (token, destination GPU)")
     ap.add_argument("--profile", action="store_true",
                     help="single GPU only: run warm-up + steps of the device-resident step and exit (for ncu)")
     ap.add_argument("--sweep", action="store_true",

@@ -177,6 +177,34 @@ int tgo_ep_pull(void* const* peer_ptrs, int64_t world, const int32_t* dst_rank, 
                 const float* weights, void* out, int64_t n_out, int64_t group, int64_t width,
                 void* stream);
 
+/* Token-level exchange: with top-k routing several of a token's experts usually sit on the same
+ * GPU, so a token's row is sent once per destination GPU (not once per routed pair) and one
+ * partial gradient sum per GPU comes back; the owner replicates rows into / reduces rows out of
+ * its expert-major buffers locally.  Token t of rank r owns slot r * tokens_per_rank + t in every
+ * GPU's token buffers ([world * tokens_per_rank][width] bf16).  No counterpart in the reference.
+ *
+ *  tgo_ep_token_maps      after tgo_ep_plan: writes, on every owner g, slot_rows[g][slot][s] (the row
+ *                         of the slot's s-th routed pair on g, or -1; int32 [world*tokens_per_rank][top_k])
+ *                         and, on the pair's owner, row_slot[owner][row] = slot (int32 [capacity]);
+ *  tgo_ep_dispatch_tokens writes src[t] into the token buffer of every GPU that owns one of t's experts;
+ *  tgo_ep_expand          owner side: rows[row] = token_buffer[row_slot[row]] for row < *n_rows_device
+ *                         (a device int32, e.g. the last cumulative offset of tgo_ep_plan);
+ *  tgo_ep_reduce          owner side: partial_sums[slot] = sum of rows[slot_rows[slot][s]] (fp32, one rounding);
+ *  tgo_ep_pull_tokens     out[t] = sum over the GPUs owning one of t's experts of their partial_sums[slot]. */
+int tgo_ep_token_maps(const int32_t* dst_rank, const int32_t* dst_row, int64_t tokens, int64_t top_k,
+                      int64_t my_rank, int64_t tokens_per_rank, void* const* row_slot_ptrs,
+                      void* const* slot_rows_ptrs, int64_t world, void* stream);
+int tgo_ep_dispatch_tokens(const void* src, const int32_t* dst_rank, int64_t tokens, int64_t top_k,
+                           int64_t width, int64_t my_rank, int64_t tokens_per_rank,
+                           void* const* token_buffer_ptrs, int64_t world, void* stream);
+int tgo_ep_expand(const void* token_buffer, const int32_t* row_slot, const int32_t* n_rows_device,
+                  void* rows, int64_t capacity, int64_t width, void* stream);
+int tgo_ep_reduce(const void* rows, const int32_t* slot_rows, int64_t n_slots, int64_t top_k,
+                  void* partial_sums, int64_t width, void* stream);
+int tgo_ep_pull_tokens(void* const* partial_sum_ptrs, int64_t world, const int32_t* dst_rank,
+                       int64_t tokens, int64_t top_k, int64_t my_rank, int64_t tokens_per_rank,
+                       void* out, int64_t width, void* stream);
+
 /* Grouped forward for callers that cannot hand over a workspace and must not trigger a device
  * allocation: the same operation and results as tgo_grouped_fwd, with the tile list kept in a
  * fixed array inside the library instead of caller memory.  No counterpart in the reference.

@@ -58,6 +58,31 @@ def test_virtual_ranks_dispatch_matmul_pull(cuda, world):
         wl = wdev[o * EL:(o + 1) * EL].contiguous()
         native.grouped_fwd(x_in[o], wl, None, y_out[o], None, plans[o][2], plans[o][3], EL, cap, N, K, qt, ws)
         native.grouped_dx(dy_in[o], None, wl, None, dx_out[o], plans[o][2], plans[o][3], EL, cap, N, K, qt, ws)
+    # token-level exchange: one row per (token, destination GPU); the owner replicates / reduces
+    slots = world * tokens
+    tok_in = [torch.full((slots, K), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    dx_part = [torch.full((slots, K), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    row_slot = [torch.full((cap,), -7, dtype=torch.int32, device="cuda") for _ in range(world)]
+    slot_rows = [torch.full((slots, top_k), -1, dtype=torch.int32, device="cuda") for _ in range(world)]
+    for r in range(world):
+        native.ep_token_maps(plans[r][0], plans[r][1], tokens, top_k, r, tokens, ptrs(row_slot), ptrs(slot_rows))
+        native.ep_dispatch_tokens(to_dev(xs[r]), plans[r][0], top_k, r, tokens, ptrs(tok_in))
+    for o in range(world):
+        n = int(plans[o][3][-1].item())
+        x2 = torch.full((cap, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+        native.ep_expand(tok_in[o], row_slot[o], plans[o][3][EL - 1:], x2)
+        torch.cuda.synchronize()
+        assert np.array_equal(bits(x2[:n]), bits(x_in[o][:n]))          # same rows as the pair-level dispatch
+        assert torch.isnan(x2[n:]).all()                                 # nothing written past the rows that exist
+        native.ep_reduce(dx_out[o], slot_rows[o], top_k, dx_part[o])
+    for r in range(world):
+        dx_tok = torch.empty(tokens, K, dtype=torch.bfloat16, device="cuda")
+        native.ep_pull_tokens(ptrs(dx_part), plans[r][0], top_k, r, tokens, dx_tok)
+        f = ids[r].reshape(-1)
+        want_dx = torch.zeros(tokens, K)
+        for i in range(f.size):
+            want_dx[i // top_k] += dys[r][i].float() @ W[f[i]]
+        assert ref.rel_frobenius(dx_tok.float().cpu(), want_dx) < DX_TOL
     gate = torch.rand(tokens, top_k)
     for r in range(world):
         y = torch.empty(tokens * top_k, N, dtype=torch.bfloat16, device="cuda")
@@ -89,7 +114,8 @@ def test_capacity_overflow_is_flagged_not_written(cuda):
     assert kept.sum() == cap and int(dst_row.max().item()) == cap - 1
 
 
-def test_single_rank_wrapper(cuda):
+@pytest.mark.parametrize("token_level", [False, True])
+def test_single_rank_wrapper(cuda, token_level):
     from torch_ggml_ops_b200.peer_parallel import PeerExpertParallel
 
     qt, E, N, K, tokens, top_k = ref.Q5_K, 8, 128, 512, 100, 2
@@ -98,8 +124,10 @@ def test_single_rank_wrapper(cuda):
     ids = blocks.topk_routing(tokens, E, top_k, seed=2)
     x = blocks.gaussian_bf16((tokens, K), 5)
     dy = blocks.gaussian_bf16((tokens * top_k, N), 6)
-    pep = PeerExpertParallel(to_dev(w), qt, E, N, K, capacity_rows=512)
+    pep = PeerExpertParallel(to_dev(w), qt, E, N, K, capacity_rows=512, tokens_per_rank=tokens if token_level else None,
+                             top_k=top_k)
     plan = pep.plan(to_dev(torch.from_numpy(ids)))
+    assert plan["token_level"] == token_level
     y = pep.forward(plan, to_dev(x))
     dx = pep.grad_input(plan, to_dev(dy))
     f = ids.reshape(-1)

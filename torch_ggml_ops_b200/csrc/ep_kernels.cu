@@ -130,6 +130,126 @@ __global__ void __launch_bounds__(256) ep_pull_kernel(const __grid_constant__ Pe
     }
 }
 
+// ---------------------------------------------------------------- token-level exchange
+// With top-k routing a token usually has several experts on the same GPU.  The kernels below move
+// a token's row once per destination GPU instead of once per routed pair, and bring back one
+// partial sum per GPU instead of one gradient row per pair: the owner replicates / reduces locally
+// at HBM speed.  Token t of rank r has the fixed slot r * tokens_per_rank + t in every owner's
+// token buffers, so no counting or extra collective is needed.
+
+// Plan time, one thread per routed pair i = t * top_k + s of this rank: tell every owner g which
+// of its rows belong to the token's slot (slot_rows[g][slot][s] = row or -1) and tell the pair's
+// owner which slot feeds that row (row_slot[owner][row] = slot).
+__global__ void __launch_bounds__(256) ep_token_maps_kernel(const int32_t* __restrict__ dst_rank, const int32_t* __restrict__ dst_row,
+                                                            long long n_pairs, int top_k, int world, long long slot0,
+                                                            const __grid_constant__ PeerPtrs row_slot,
+                                                            const __grid_constant__ PeerPtrs slot_rows) {
+    const long long i = blockIdx.x * 256LL + threadIdx.x;
+    if (i >= n_pairs) return;
+    const long long t = i / top_k;
+    const int s = static_cast<int>(i - t * top_k);
+    const int r = dst_rank[i], row = dst_row[i];
+    const long long slot = slot0 + t;
+    for (int g = 0; g < world; ++g) static_cast<int32_t*>(slot_rows.p[g])[slot * top_k + s] = (r == g) ? row : -1;
+    if (r >= 0) static_cast<int32_t*>(row_slot.p[r])[row] = static_cast<int32_t>(slot);
+}
+
+// tok[g][slot][:] = src[t][:] for every GPU g that owns at least one of token t's experts.
+__global__ void __launch_bounds__(256) ep_dispatch_tokens_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ dst_rank,
+                                                                 long long tokens, int top_k, int vec_per_row, long long slot0,
+                                                                 const __grid_constant__ PeerPtrs tok) {
+    const long long total = tokens * vec_per_row;
+    for (long long v = blockIdx.x * 256LL + threadIdx.x; v < total; v += 256LL * gridDim.x) {
+        const long long t = v / vec_per_row;
+        const int c = static_cast<int>(v - t * vec_per_row);
+        const uint4 val = src[v];
+        unsigned long long seen = 0ull;
+        for (int s = 0; s < top_k; ++s) {
+            const int r = dst_rank[t * top_k + s];
+            if (r < 0 || ((seen >> r) & 1ull)) continue;
+            seen |= 1ull << r;
+            static_cast<uint4*>(tok.p[r])[(slot0 + t) * vec_per_row + c] = val;
+        }
+    }
+}
+
+// Owner side: rows[row][:] = tok[row_slot[row]][:] for the rows that exist (*n_rows, a device value).
+__global__ void __launch_bounds__(256) ep_expand_kernel(const uint4* __restrict__ tok, const int32_t* __restrict__ row_slot,
+                                                        const int32_t* __restrict__ n_rows, uint4* __restrict__ rows,
+                                                        long long capacity, int vec_per_row) {
+    long long n = *n_rows;
+    if (n > capacity) n = capacity;
+    const long long total = n * vec_per_row;
+    for (long long v = blockIdx.x * 256LL + threadIdx.x; v < total; v += 256LL * gridDim.x) {
+        const long long row = v / vec_per_row;
+        const int c = static_cast<int>(v - row * vec_per_row);
+        rows[v] = tok[static_cast<long long>(row_slot[row]) * vec_per_row + c];
+    }
+}
+
+// Owner side: part[slot][:] = sum over the slot's rows of rows[row][:] (fp32, rounded once); slots
+// without a row on this GPU are left alone (nobody reads them).
+__global__ void __launch_bounds__(256) ep_reduce_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ slot_rows,
+                                                        long long n_slots, int top_k, uint4* __restrict__ part, int vec_per_row) {
+    const long long total = n_slots * vec_per_row;
+    for (long long v = blockIdx.x * 256LL + threadIdx.x; v < total; v += 256LL * gridDim.x) {
+        const long long slot = v / vec_per_row;
+        const int c = static_cast<int>(v - slot * vec_per_row);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        bool any = false;
+        for (int s = 0; s < top_k; ++s) {
+            const int row = slot_rows[slot * top_k + s];
+            if (row < 0) continue;
+            any = true;
+            const uint4 val = rows[static_cast<long long>(row) * vec_per_row + c];
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&val);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
+            }
+        }
+        if (!any) continue;
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        part[v] = o;
+    }
+}
+
+// out[t][:] = sum over the GPUs g that own one of token t's experts of part[g][slot][:] (fp32).
+__global__ void __launch_bounds__(256) ep_pull_tokens_kernel(const __grid_constant__ PeerPtrs part, const int32_t* __restrict__ dst_rank,
+                                                             long long tokens, int top_k, int vec_per_row, long long slot0,
+                                                             uint4* __restrict__ out) {
+    const long long total = tokens * vec_per_row;
+    for (long long v = blockIdx.x * 256LL + threadIdx.x; v < total; v += 256LL * gridDim.x) {
+        const long long t = v / vec_per_row;
+        const int c = static_cast<int>(v - t * vec_per_row);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        unsigned long long seen = 0ull;
+        for (int s = 0; s < top_k; ++s) {
+            const int r = dst_rank[t * top_k + s];
+            if (r < 0 || ((seen >> r) & 1ull)) continue;
+            seen |= 1ull << r;
+            const uint4 val = static_cast<const uint4*>(part.p[r])[(slot0 + t) * vec_per_row + c];
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&val);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
+            }
+        }
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        out[v] = o;
+    }
+}
+
 static int ep_grid(long long work_items) {
     long long blocks = (work_items + 255) / 256;
     if (blocks > 148LL * 8) blocks = 148LL * 8;
@@ -206,6 +326,79 @@ int tgo_ep_pull(void* const* peer_ptrs, int64_t world, const int32_t* dst_rank, 
     ep_pull_kernel<<<ep_grid(n_out * vec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         pp, dst_rank, dst_row, weights, static_cast<uint4*>(out), n_out, static_cast<int>(group), vec);
     return ep_launch_check("ep_pull_kernel launch failed");
+}
+
+int tgo_ep_token_maps(const int32_t* dst_rank, const int32_t* dst_row, int64_t tokens, int64_t top_k, int64_t my_rank,
+                      int64_t tokens_per_rank, void* const* row_slot_ptrs, void* const* slot_rows_ptrs, int64_t world,
+                      void* stream) {
+    if (dst_rank == nullptr || dst_row == nullptr) return route_fail(TGO_E_ARG, "null pointer");
+    if (tokens <= 0 || top_k <= 0 || top_k > 1024 || tokens > tokens_per_rank || my_rank < 0 || my_rank >= world ||
+        tokens_per_rank * world * top_k > INT32_MAX)
+        return route_fail(TGO_E_ARG, "token maps need 0 < tokens <= tokens_per_rank, 0 < top_k <= 1024 and the rank inside the world");
+    PeerPtrs rs = {}, sr = {};
+    int rc = fill_peers(rs, row_slot_ptrs, world);
+    if (rc == TGO_OK) rc = fill_peers(sr, slot_rows_ptrs, world);
+    if (rc != TGO_OK) return rc;
+    const long long n_pairs = tokens * top_k;
+    ep_token_maps_kernel<<<static_cast<int>((n_pairs + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        dst_rank, dst_row, n_pairs, static_cast<int>(top_k), static_cast<int>(world), my_rank * tokens_per_rank, rs, sr);
+    return ep_launch_check("ep_token_maps_kernel launch failed");
+}
+
+int tgo_ep_dispatch_tokens(const void* src, const int32_t* dst_rank, int64_t tokens, int64_t top_k, int64_t width,
+                           int64_t my_rank, int64_t tokens_per_rank, void* const* token_buffer_ptrs, int64_t world,
+                           void* stream) {
+    if (src == nullptr || dst_rank == nullptr) return route_fail(TGO_E_ARG, "null pointer");
+    if (tokens <= 0 || top_k <= 0 || tokens > tokens_per_rank || width <= 0 || (width * 2) % 16 != 0 || my_rank < 0 ||
+        my_rank >= world)
+        return route_fail(TGO_E_ARG, "token dispatch needs 0 < tokens <= tokens_per_rank, a row length that is a multiple of 8 and the rank inside the world");
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) != 0) return route_fail(TGO_E_ARG, "src must be 16-byte aligned");
+    PeerPtrs pp = {};
+    const int rc = fill_peers(pp, token_buffer_ptrs, world);
+    if (rc != TGO_OK) return rc;
+    const int vec = static_cast<int>(width / 8);
+    ep_dispatch_tokens_kernel<<<ep_grid(tokens * vec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(src), dst_rank, tokens, static_cast<int>(top_k), vec, my_rank * tokens_per_rank, pp);
+    return ep_launch_check("ep_dispatch_tokens_kernel launch failed");
+}
+
+int tgo_ep_expand(const void* token_buffer, const int32_t* row_slot, const int32_t* n_rows_device, void* rows,
+                  int64_t capacity, int64_t width, void* stream) {
+    if (token_buffer == nullptr || row_slot == nullptr || n_rows_device == nullptr || rows == nullptr)
+        return route_fail(TGO_E_ARG, "null pointer");
+    if (capacity <= 0 || width <= 0 || (width * 2) % 16 != 0)
+        return route_fail(TGO_E_ARG, "expand needs capacity > 0 and a row length that is a multiple of 8");
+    const int vec = static_cast<int>(width / 8);
+    ep_expand_kernel<<<ep_grid(capacity * vec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(token_buffer), row_slot, n_rows_device, static_cast<uint4*>(rows), capacity, vec);
+    return ep_launch_check("ep_expand_kernel launch failed");
+}
+
+int tgo_ep_reduce(const void* rows, const int32_t* slot_rows, int64_t n_slots, int64_t top_k, void* partial_sums,
+                  int64_t width, void* stream) {
+    if (rows == nullptr || slot_rows == nullptr || partial_sums == nullptr) return route_fail(TGO_E_ARG, "null pointer");
+    if (n_slots <= 0 || top_k <= 0 || width <= 0 || (width * 2) % 16 != 0)
+        return route_fail(TGO_E_ARG, "reduce needs slots > 0, top_k > 0 and a row length that is a multiple of 8");
+    const int vec = static_cast<int>(width / 8);
+    ep_reduce_kernel<<<ep_grid(n_slots * vec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(rows), slot_rows, n_slots, static_cast<int>(top_k), static_cast<uint4*>(partial_sums), vec);
+    return ep_launch_check("ep_reduce_kernel launch failed");
+}
+
+int tgo_ep_pull_tokens(void* const* partial_sum_ptrs, int64_t world, const int32_t* dst_rank, int64_t tokens, int64_t top_k,
+                       int64_t my_rank, int64_t tokens_per_rank, void* out, int64_t width, void* stream) {
+    if (dst_rank == nullptr || out == nullptr) return route_fail(TGO_E_ARG, "null pointer");
+    if (tokens <= 0 || top_k <= 0 || tokens > tokens_per_rank || width <= 0 || (width * 2) % 16 != 0 || my_rank < 0 ||
+        my_rank >= world)
+        return route_fail(TGO_E_ARG, "token pull needs 0 < tokens <= tokens_per_rank, a row length that is a multiple of 8 and the rank inside the world");
+    if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return route_fail(TGO_E_ARG, "out must be 16-byte aligned");
+    PeerPtrs pp = {};
+    const int rc = fill_peers(pp, partial_sum_ptrs, world);
+    if (rc != TGO_OK) return rc;
+    const int vec = static_cast<int>(width / 8);
+    ep_pull_tokens_kernel<<<ep_grid(tokens * vec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        pp, dst_rank, tokens, static_cast<int>(top_k), vec, my_rank * tokens_per_rank, static_cast<uint4*>(out));
+    return ep_launch_check("ep_pull_tokens_kernel launch failed");
 }
 
 }  // extern "C"

@@ -38,7 +38,8 @@ __global__ void __launch_bounds__(kRouteBlock) route_count_kernel(const int32_t*
 }
 
 // Pass 2 (one block): per expert, exclusive prefix over the blocks; then the prefix over experts.
-// block_counts[b][e] becomes the first sorted row of block b's pairs for expert e.
+// block_counts[b][e] becomes the first row of block b's pairs for expert e inside that expert's
+// run of sorted rows (the scatter pass adds the expert's first row, expert_offsets[e - 1]).
 __global__ void __launch_bounds__(1024) route_scan_kernel(int32_t* __restrict__ block_counts, int num_blocks,
                                                           int num_experts, int64_t* __restrict__ expert_indices,
                                                           int32_t* __restrict__ expert_offsets,
@@ -47,7 +48,19 @@ __global__ void __launch_bounds__(1024) route_scan_kernel(int32_t* __restrict__ 
     __shared__ int32_t warp_sums[32];
     for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
         int32_t run = 0;
-        for (int b = 0; b < num_blocks; ++b) {
+        int b = 0;
+        // sixteen independent loads in flight per round trip to L2, then the running sum
+        for (; b + 16 <= num_blocks; b += 16) {
+            int32_t v[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) v[u] = block_counts[static_cast<size_t>(b + u) * num_experts + e];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                block_counts[static_cast<size_t>(b + u) * num_experts + e] = run;
+                run += v[u];
+            }
+        }
+        for (; b < num_blocks; ++b) {
             const size_t k = static_cast<size_t>(b) * num_experts + e;
             const int32_t v = block_counts[k];
             block_counts[k] = run;
@@ -90,20 +103,17 @@ __global__ void __launch_bounds__(1024) route_scan_kernel(int32_t* __restrict__ 
         carry += warp_sums[nwarps - 1];
         __syncthreads();
     }
-    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
-        const int32_t base = totals[e];
-        for (int b = 0; b < num_blocks; ++b) block_counts[static_cast<size_t>(b) * num_experts + e] += base;
-    }
 }
 
 // Pass 3: stable placement.  Warps of a block take turns so that earlier pairs get earlier rows.
 __global__ void __launch_bounds__(kRouteBlock) route_scatter_kernel(const int32_t* __restrict__ ids, int n, int num_experts,
                                                                     const int32_t* __restrict__ block_starts,
+                                                                    const int32_t* __restrict__ expert_offsets,
                                                                     int32_t* __restrict__ sorted_to_pair,
                                                                     int32_t* __restrict__ pair_to_sorted) {
     extern __shared__ int32_t cursor[];
     for (int e = threadIdx.x; e < num_experts; e += kRouteBlock)
-        cursor[e] = block_starts[static_cast<size_t>(blockIdx.x) * num_experts + e];
+        cursor[e] = block_starts[static_cast<size_t>(blockIdx.x) * num_experts + e] + (e > 0 ? expert_offsets[e - 1] : 0);
     __syncthreads();
     const int i = blockIdx.x * kRouteBlock + threadIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -266,7 +276,7 @@ int tgo_route_sort(const int32_t* expert_ids, int64_t n_pairs, int64_t num_exper
     int32_t* counts = static_cast<int32_t*>(workspace);
     route_count_kernel<<<blocks, kRouteBlock, E * sizeof(int32_t), s>>>(expert_ids, n, E, counts);
     route_scan_kernel<<<1, 1024, 0, s>>>(counts, blocks, E, expert_indices, expert_offsets, expert_counts);
-    route_scatter_kernel<<<blocks, kRouteBlock, E * sizeof(int32_t), s>>>(expert_ids, n, E, counts, sorted_to_pair,
+    route_scatter_kernel<<<blocks, kRouteBlock, E * sizeof(int32_t), s>>>(expert_ids, n, E, counts, expert_offsets, sorted_to_pair,
                                                                          pair_to_sorted);
     return launch_check("routing kernel launch failed");
 }

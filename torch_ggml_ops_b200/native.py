@@ -36,6 +36,11 @@ SIGNATURES = {
     "tgo_ep_plan": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tgo_ep_dispatch": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _vp, _i64, _vp]),
     "tgo_ep_pull": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "tgo_ep_token_maps": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp]),
+    "tgo_ep_dispatch_tokens": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "tgo_ep_expand": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
+    "tgo_ep_reduce": (_i32, [_vp, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "tgo_ep_pull_tokens": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tgo_grouped_fwd_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
 }
 
@@ -230,3 +235,35 @@ def ep_dispatch(src, divisor, dst_rank, dst_row, peer_ptrs, stream=None) -> None
 def ep_pull(peer_ptrs, dst_rank, dst_row, out, group=1, weights=None, stream=None) -> None:
     check(lib().tgo_ep_pull(_ptr_array(peer_ptrs), len(peer_ptrs), _ptr(dst_rank), _ptr(dst_row), _ptr(weights),
                             _ptr(out), out.shape[0], group, out.shape[1], _stream(stream)), "tgo_ep_pull")
+
+
+def ep_token_maps(dst_rank, dst_row, tokens, top_k, my_rank, tokens_per_rank, row_slot_ptrs, slot_rows_ptrs,
+                  stream=None) -> None:
+    """Token-level exchange, plan time: per-slot row lists on every owner and the row -> slot map on
+    each pair's owner; see ``tgo_ep_token_maps``."""
+    check(lib().tgo_ep_token_maps(_ptr(dst_rank), _ptr(dst_row), tokens, top_k, my_rank, tokens_per_rank,
+                                  _ptr_array(row_slot_ptrs), _ptr_array(slot_rows_ptrs), len(row_slot_ptrs),
+                                  _stream(stream)), "tgo_ep_token_maps")
+
+
+def ep_dispatch_tokens(src, dst_rank, top_k, my_rank, tokens_per_rank, token_buffer_ptrs, stream=None) -> None:
+    check(lib().tgo_ep_dispatch_tokens(_ptr(src), _ptr(dst_rank), src.shape[0], top_k, src.shape[1], my_rank,
+                                       tokens_per_rank, _ptr_array(token_buffer_ptrs), len(token_buffer_ptrs),
+                                       _stream(stream)), "tgo_ep_dispatch_tokens")
+
+
+def ep_expand(token_buffer, row_slot, n_rows_device, rows, stream=None) -> None:
+    """rows[r] = token_buffer[row_slot[r]] for r < n_rows_device[0] (a device int32 tensor)."""
+    check(lib().tgo_ep_expand(_ptr(token_buffer), _ptr(row_slot), _ptr(n_rows_device), _ptr(rows), rows.shape[0],
+                              rows.shape[1], _stream(stream)), "tgo_ep_expand")
+
+
+def ep_reduce(rows, slot_rows, top_k, partial_sums, stream=None) -> None:
+    check(lib().tgo_ep_reduce(_ptr(rows), _ptr(slot_rows), partial_sums.shape[0], top_k, _ptr(partial_sums),
+                              rows.shape[1], _stream(stream)), "tgo_ep_reduce")
+
+
+def ep_pull_tokens(partial_sum_ptrs, dst_rank, top_k, my_rank, tokens_per_rank, out, stream=None) -> None:
+    check(lib().tgo_ep_pull_tokens(_ptr_array(partial_sum_ptrs), len(partial_sum_ptrs), _ptr(dst_rank), out.shape[0],
+                                   top_k, my_rank, tokens_per_rank, _ptr(out), out.shape[1], _stream(stream)),
+          "tgo_ep_pull_tokens")

@@ -12,7 +12,14 @@ Rows cross NVLink exactly once per exchange, written (dispatch) or read (pull) b
 peer stores / loads straight into / out of the expert-major layout the grouped kernels consume, so
 there is no permutation pass on either side and no host read of the routing: the grouped kernels
 are launched over the whole receive buffer (`capacity` rows) and the device-side group offsets say
-which rows exist.  "fence" is a stream-ordered one-element all-reduce: it orders the ranks'
+which rows exist.
+
+Token-level exchange (when ``tokens_per_rank`` and ``top_k`` are given): the two wide exchanges
+move one row per (token, destination GPU) instead of one per routed pair - a token's row goes once
+to every GPU that owns one of its experts and is replicated into the expert-major buffer there
+(tgo_ep_dispatch_tokens + tgo_ep_expand), and the input gradient comes back as one partial sum per
+GPU (tgo_ep_reduce + tgo_ep_pull_tokens).  With 8 experts per token this cuts the NVLink bytes of
+those exchanges by 4x on 2 GPUs and 2.2x on 4.  "fence" is a stream-ordered one-element all-reduce: it orders the ranks'
 phases without any spin-wait in our kernels.  Multicast is never used (the symmetric-memory
 allocator is told not to bind a multicast object).
 
@@ -35,7 +42,8 @@ class PeerExpertParallel:
     ``quant_type``; ``local_weight`` is this rank's shard [E / world, N, row_bytes] (uint8, CUDA)."""
 
     def __init__(self, local_weight: torch.Tensor, quant_type: int, num_experts: int, out_features: int,
-                 in_features: int, capacity_rows: int, group=None):
+                 in_features: int, capacity_rows: int, group=None, tokens_per_rank: int | None = None,
+                 top_k: int | None = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -48,23 +56,37 @@ class PeerExpertParallel:
         self.N, self.K, self.cap = int(out_features), int(in_features), int(capacity_rows)
         dev = local_weight.device
         self.device = dev
-        shapes = {"x_in": self.K, "y_out": self.N, "dy_in": self.N, "dx_out": self.K}
+        # (rows, columns, dtype) of every buffer the peers address
+        shapes = {"x_in": (self.cap, self.K, torch.bfloat16), "y_out": (self.cap, self.N, torch.bfloat16),
+                  "dy_in": (self.cap, self.N, torch.bfloat16), "dx_out": (self.cap, self.K, torch.bfloat16)}
+        self.token_level = tokens_per_rank is not None and top_k is not None
+        if self.token_level:
+            self.tpr, self.top_k = int(tokens_per_rank), int(top_k)
+            slots = self.world * self.tpr
+            shapes.update({"tok_in": (slots, self.K, torch.bfloat16), "dx_part": (slots, self.K, torch.bfloat16),
+                           "row_slot": (self.cap, 1, torch.int32), "slot_rows": (slots, self.top_k, torch.int32)})
         self.buf, self.peers = {}, {}
         if self.world > 1:
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             import torch.distributed._symmetric_memory as symm_mem
 
-            for name, width in shapes.items():
-                t = symm_mem.empty(self.cap, width, dtype=torch.bfloat16, device=dev)
+            for name, (rows, cols, dtype) in shapes.items():
+                t = symm_mem.empty(rows, cols, dtype=dtype, device=dev)
                 hdl = symm_mem.rendezvous(t, dist.group.WORLD if group is None else group)
                 self.buf[name] = t
                 self.peers[name] = [int(p) for p in hdl.buffer_ptrs]
                 self.buf[name + "_hdl"] = hdl  # keeps the mapping alive
         else:
-            for name, width in shapes.items():
-                t = torch.empty(self.cap, width, dtype=torch.bfloat16, device=dev)
+            for name, (rows, cols, dtype) in shapes.items():
+                t = torch.empty(rows, cols, dtype=dtype, device=dev)
                 self.buf[name] = t
                 self.peers[name] = [t.data_ptr()]
+        if self.token_level:
+            # a slot nobody has written yet must not name a row; peers write into this buffer from
+            # their first plan on, so everybody finishes the fill before anybody goes on
+            self.buf["slot_rows"].fill_(-1)
+            if self.world > 1:
+                dist.barrier(group=group)
         self.ws = torch.empty(native.grouped_workspace_bytes(self.cap, self.EL), dtype=torch.uint8, device=dev)
         self._token = torch.zeros(1, dtype=torch.int32, device=dev)
         self.overflow = None
@@ -107,15 +129,28 @@ class PeerExpertParallel:
             counts_all = b["counts"].reshape(1, self.E)
         dst_rank, dst_row, li, lo, overflow = native.ep_plan(counts_all, self.rank, flat, p2s, self.cap, out=b)
         self.overflow = overflow  # device flag: a row did not fit in `capacity_rows` (read it when convenient)
-        return {"top_k": topk_ids.shape[1], "dst_rank": dst_rank, "dst_row": dst_row, "indices": li, "offsets": lo}
+        plan = {"top_k": topk_ids.shape[1], "tokens": topk_ids.shape[0], "dst_rank": dst_rank, "dst_row": dst_row,
+                "indices": li, "offsets": lo, "token_level": False}
+        if self.token_level and plan["top_k"] == self.top_k and plan["tokens"] <= self.tpr:
+            # the peers' maps are rewritten here; the exchanges that read them come after a fence
+            native.ep_token_maps(dst_rank, dst_row, plan["tokens"], self.top_k, self.rank, self.tpr,
+                                 self.peers["row_slot"], self.peers["slot_rows"])
+            plan["token_level"] = True
+            plan["n_rows"] = lo[self.EL - 1:]   # device int32: rows that exist in this rank's buffers
+        return plan
 
     # ------------------------------------------------------------------ forward
     def forward(self, plan, x_tokens: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """[tokens, K] bf16 -> [tokens * top_k, N]: every routed pair's expert projection
         (written to ``out`` when given)."""
         k = plan["top_k"]
-        native.ep_dispatch(x_tokens, k, plan["dst_rank"], plan["dst_row"], self.peers["x_in"])
-        self._fence()
+        if plan["token_level"]:
+            native.ep_dispatch_tokens(x_tokens, plan["dst_rank"], k, self.rank, self.tpr, self.peers["tok_in"])
+            self._fence()
+            native.ep_expand(self.buf["tok_in"], self.buf["row_slot"], plan["n_rows"], self.buf["x_in"])
+        else:
+            native.ep_dispatch(x_tokens, k, plan["dst_rank"], plan["dst_row"], self.peers["x_in"])
+            self._fence()
         native.grouped_fwd(self.buf["x_in"], self.weight, None, self.buf["y_out"], None, plan["indices"],
                            plan["offsets"], self.EL, self.cap, self.N, self.K, self.qt, self.ws)
         self._fence()
@@ -134,9 +169,14 @@ class PeerExpertParallel:
         self._fence()
         native.grouped_dx(self.buf["dy_in"], None, self.weight, None, self.buf["dx_out"], plan["indices"],
                           plan["offsets"], self.EL, self.cap, self.N, self.K, self.qt, self.ws)
-        self._fence()
         dx = out if out is not None else torch.empty(dy_pairs.shape[0] // k, self.K, dtype=torch.bfloat16,
                                                       device=self.device)
+        if plan["token_level"] and weights is None:
+            native.ep_reduce(self.buf["dx_out"], self.buf["slot_rows"], k, self.buf["dx_part"])
+            self._fence()
+            native.ep_pull_tokens(self.peers["dx_part"], plan["dst_rank"], k, self.rank, self.tpr, dx)
+            return dx
+        self._fence()
         w = None if weights is None else weights.reshape(-1).float().contiguous()
         native.ep_pull(self.peers["dx_out"], plan["dst_rank"], plan["dst_row"], dx, k, w)
         return dx
