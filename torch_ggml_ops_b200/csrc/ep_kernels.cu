@@ -25,24 +25,31 @@ __global__ void __launch_bounds__(1024) ep_offsets_kernel(const int32_t* __restr
                                                           int32_t* __restrict__ dst_base, int32_t* __restrict__ seg_start,
                                                           int64_t* __restrict__ local_indices,
                                                           int32_t* __restrict__ local_offsets) {
+    // per expert: rows from all sources, rows from the sources before this rank, this rank's rows
+    __shared__ int32_t total[4096], earlier[4096], mine[4096];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int t = 0, b = 0;
+        for (int s = 0; s < W; ++s) {
+            const int c = counts[s * E + e];
+            if (s < me) b += c;
+            t += c;
+        }
+        total[e] = t;
+        earlier[e] = b;
+        mine[e] = counts[me * E + e];
+    }
+    __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         const int first = (e / EL) * EL;
         int before_experts = 0;   // rows of earlier experts of the same owner, all sources
-        for (int f = first; f < e; ++f)
-            for (int s = 0; s < W; ++s) before_experts += counts[s * E + f];
-        int before_sources = 0, total = 0;
-        for (int s = 0; s < W; ++s) {
-            const int c = counts[s * E + e];
-            if (s < me) before_sources += c;
-            total += c;
-        }
-        dst_base[e] = before_experts + before_sources;
+        for (int f = first; f < e; ++f) before_experts += total[f];
         int mine_before = 0;
-        for (int f = 0; f < e; ++f) mine_before += counts[me * E + f];
+        for (int f = 0; f < e; ++f) mine_before += mine[f];
+        dst_base[e] = before_experts + earlier[e];
         seg_start[e] = mine_before;
         if (e / EL == me) {
             local_indices[e - first] = e - first;
-            local_offsets[e - first] = before_experts + total;
+            local_offsets[e - first] = before_experts + total[e];
         }
     }
 }

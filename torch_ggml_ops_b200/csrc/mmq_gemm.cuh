@@ -30,9 +30,10 @@
 //   full[j % NB]  <- the activation TMA (expect_tx for the whole stage, announced by the leader)
 //                    and the decode warps of the stage's steps (of both CTAs); the UMMA issuer
 //                    waits on it once and issues the stage's 4 * KS UMMAs;
-//   done[j % NB]  <- one tcgen05.commit after those UMMAs (one per CTA of a pair); the activation
-//                    producer waits on it before refilling the slot, the decode warps of stage
-//                    j + NA wait on it before overwriting decoded-weight slot j % NA (NA <= NB);
+//   done[j % NB]  <- one tcgen05.commit after those UMMAs (one per CTA of a pair).  Operands live
+//                    in rings of one-step slots (NBS activation slots, NAS decoded-weight slots):
+//                    whoever refills the slot of step i waits for done of the stage that held step
+//                    i - NBS (activation producer) or i - NAS (decode warps);
 //   raw_full / raw_empty: TMA raw-block ring <-> decode;  acc_full / acc_empty: TMEM <-> epilogue.
 // All waits are bounded (ptx.cuh); a wait that gives up unwinds every role to the common exit,
 // which frees TMEM and records a status code.
@@ -49,21 +50,22 @@ constexpr int kTileM = 128;          // weight-side extent of one tile (TMEM lan
 constexpr int kTileTok = 256;        // most tokens per tile (TMEM columns of one accumulator)
 constexpr int kStepK = 64;           // reduction elements per pipeline step (one swizzle row)
 constexpr int kWgtTileBytes = kTileM * 128;
-// Ring depths.  One CTA: 4 activation stages of 32 KB, up to 3 decoded-weight stages.  CTA pair:
-// each CTA stages only its half of the tokens (16 KB), which buys deeper rings from the same
-// shared memory: the credit of a stage is away for a TMA round trip plus the UMMAs plus two
-// barrier hops (about 2500 cycles), so depth, not bandwidth, is what keeps the tensor pipe fed.
+// Ring depths, in slots of one step (the barriers are per stage).  One CTA: 4 activation slots of
+// 32 KB, up to 3 decoded-weight slots of 16 KB.  CTA pair: each CTA stages only its half of the
+// tokens (16 KB per slot), which buys deeper rings from the same shared memory; measured on the
+// grouped benchmark, six activation slots (a TMA round trip is ~1500-2000 cycles) and five
+// decoded-weight slots beat 5/6, 7/4 and 4/7.
 #ifndef TGO_ACT_STAGES
 #define TGO_ACT_STAGES 4
 #endif
 #ifndef TGO_WGT_STAGES_MAX
 #define TGO_WGT_STAGES_MAX 3
 #endif
-#ifndef TGO_PAIR_ACT_STAGES
-#define TGO_PAIR_ACT_STAGES 3
+#ifndef TGO_PAIR_ACT_SLOTS
+#define TGO_PAIR_ACT_SLOTS 6
 #endif
-#ifndef TGO_PAIR_WGT_STAGES_MAX
-#define TGO_PAIR_WGT_STAGES_MAX 2
+#ifndef TGO_PAIR_WGT_SLOTS_MAX
+#define TGO_PAIR_WGT_SLOTS_MAX 5
 #endif
 // 64-element steps per pipeline stage ("super-step").  The UMMA issuer pays one barrier wait and
 // one commit per stage whatever its size, and every tcgen05 instruction costs that thread some
@@ -75,10 +77,10 @@ constexpr int kWgtTileBytes = kTileM * 128;
 #define TGO_PAIR_SUBSTEPS 2
 #endif
 #ifndef TGO_PAIR_RAW_STAGES_FWD
-#define TGO_PAIR_RAW_STAGES_FWD 3
+#define TGO_PAIR_RAW_STAGES_FWD 2
 #endif
 #ifndef TGO_PAIR_RAW_STAGES_BWD
-#define TGO_PAIR_RAW_STAGES_BWD 6
+#define TGO_PAIR_RAW_STAGES_BWD 4
 #endif
 constexpr int kDecodeWarps = 8;        // warps of one decode group (256 threads x 32 weights = one step)
 constexpr int kDecodeGroups = 2;       // groups take alternate steps, so two steps decode at once
@@ -144,10 +146,9 @@ struct GemmCfg {
     static_assert(kSub == 1 || kSub == kDecodeGroups, "a stage holds one step, or one step per decode group");
     static constexpr int kActRows = kTileTok / CG;              // token rows staged by one CTA
     static constexpr int kActTileBytes = kActRows * 128;        // one step of activations
-    static constexpr int kActStageBytes = kSub * kActTileBytes;
-    static constexpr int kWgtStageBytes = kSub * kWgtTileBytes;
-    static constexpr int kActStages = CG == 2 ? TGO_PAIR_ACT_STAGES : TGO_ACT_STAGES;
-    static constexpr int kWgtStagesMax = CG == 2 ? TGO_PAIR_WGT_STAGES_MAX : TGO_WGT_STAGES_MAX;
+    static constexpr int kActSlots = CG == 2 ? TGO_PAIR_ACT_SLOTS : TGO_ACT_STAGES;          // steps of activations in flight
+    static constexpr int kWgtSlotsMax = CG == 2 ? TGO_PAIR_WGT_SLOTS_MAX : TGO_WGT_STAGES_MAX;   // decoded steps in flight
+    static constexpr int kBars = 4;   // full / done barrier pairs (one per stage in flight)
     static constexpr int kTokPad = CG == 2 ? 32 : 16;           // token padding of a tile (UMMA N granularity)
     static constexpr int kRawRows = MODE == kFwd ? 128 : 64;    // block windows per raw stage
     // pair: as many raw stages as fit in about 56 KB (the raw ring has to cover an HBM round trip)
@@ -159,12 +160,13 @@ struct GemmCfg {
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kGridBytes = QT == QT_IQ2_S ? 8192 : 0;
     static constexpr int kFixed = 1024 /*alignment slack*/ + 512 /*barriers etc.*/ + 128 /*read slack*/ + kEpiStageBytes +
-                                  kActStages * kActStageBytes + kRawBytes + kGridBytes;
-    static constexpr int kWgtStagesFit = (kSmemLimit - kFixed) / kWgtStageBytes;
-    static constexpr int kWgtStagesCap = kWgtStagesMax < kActStages ? kWgtStagesMax : kActStages;
-    static constexpr int kWgtStages = kWgtStagesFit >= kWgtStagesCap ? kWgtStagesCap : kWgtStagesFit;
-    static_assert(kWgtStages >= 2, "shared memory budget");
-    static constexpr int kSmemBytes = kFixed + kWgtStages * kWgtStageBytes;
+                                  kActSlots * kActTileBytes + kRawBytes + kGridBytes;
+    static constexpr int kWgtSlotsFit = (kSmemLimit - kFixed) / kWgtTileBytes;
+    static constexpr int kWgtSlots = kWgtSlotsFit >= kWgtSlotsMax ? kWgtSlotsMax : kWgtSlotsFit;
+    static_assert(kWgtSlots > kSub && kActSlots > kSub, "shared memory budget: more than one stage must fit");
+    // a barrier is reused every kBars stages: nobody may still wait on its previous phase then
+    static_assert((kWgtSlots + kSub - 1) / kSub <= kBars && (kActSlots + kSub - 1) / kSub <= kBars, "ring deeper than the barriers");
+    static constexpr int kSmemBytes = kFixed + kWgtSlots * kWgtTileBytes;
 };
 
 struct TileInfo {
@@ -222,15 +224,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     using Cfg = GemmCfg<QT, MODE, CG>;
     using Fmt = BlockFmt<QT>;
-    constexpr int NA = Cfg::kWgtStages, NB = Cfg::kActStages, NR = Cfg::kRawStages;
-    constexpr int kActTileBytes = Cfg::kActTileBytes, kActStageBytes = Cfg::kActStageBytes;
-    constexpr int kWgtStageBytes = Cfg::kWgtStageBytes, KS = Cfg::kSub;
+    // NAS / NBS: decoded-weight and activation slots (one step each); NB: stage barriers
+    constexpr int NAS = Cfg::kWgtSlots, NBS = Cfg::kActSlots, NB = Cfg::kBars, NR = Cfg::kRawStages;
+    constexpr int kActTileBytes = Cfg::kActTileBytes, KS = Cfg::kSub;
     // CTA pair: rank 0 (the leader) owns the barriers both CTAs feed (full, acc_empty) and issues
     // the UMMAs; every CTA owns the barriers only it waits on (done, raw, acc_full).
     const int rank = CG == 2 ? static_cast<int>(cluster_ctarank()) : 0;
     const int cta = CG == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
     const int ncta = CG == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-    static_assert(NA <= NB, "the decoded-weight ring may not be deeper than the step ring");
 
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -238,8 +239,8 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
 
     // carve-up (all operand tiles 1024-byte aligned)
     const uint32_t act_s = smem_base;
-    const uint32_t wgt_s = act_s + NB * kActStageBytes;
-    const uint32_t raw_s = wgt_s + NA * kWgtStageBytes;
+    const uint32_t wgt_s = act_s + NBS * kActTileBytes;
+    const uint32_t raw_s = wgt_s + NAS * kWgtTileBytes;
     const uint32_t grid_s = raw_s + Cfg::kRawBytes + 128;
     const uint32_t epi_s = grid_s + Cfg::kGridBytes;
     const uint32_t misc_s = epi_s + kEpiStageBytes;
@@ -322,8 +323,13 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     TileInfo t;
                     if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                     for (int stage = 0; stage < nstages; ++stage, ++it) {
-                        const uint32_t s = it % NB, ph = (it / NB) & 1u;
-                        if (!mbar_wait(bar_done + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty)) { ok = false; break; }
+                        const uint32_t s = it % NB;
+                        // the stage's last step reuses the slot of step (last - NBS): wait for that stage's UMMAs
+                        const uint32_t last = it * KS + (KS - 1);
+                        if (last >= static_cast<uint32_t>(NBS)) {
+                            const uint32_t jw = (last - NBS) / KS;
+                            if (!mbar_wait(bar_done + 8 * (jw % NB), (jw / NB) & 1u, abort_word, kAbortActEmpty)) { ok = false; break; }
+                        }
                         // the leader announces the bytes of the whole stage; each CTA copies its share
                         // of the token rows (all of them, or its half) and the bytes count on the
                         // leader's barrier
@@ -336,7 +342,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                             // a step past the end reads columns outside the matrix: TMA fills zeros
                             int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
                             if (step >= nsteps) { set = 0; red0 = (steps_set + (step - nsteps)) * kStepK; }
-                            uint32_t dst = act_s + s * kActStageBytes + ks * kActTileBytes;
+                            uint32_t dst = act_s + ((it * KS + ks) % NBS) * kActTileBytes;
                             int rem = t.ntok_pad / CG;
                             int row = t.row0 + rank * rem;
 #pragma unroll
@@ -364,15 +370,19 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 TileInfo t;
                 if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 for (int stage = 0; stage < nstages; ++stage, ++it) {
-                    const uint32_t s = it % NB, ph = (it / NB) & 1u;
-                    if (!lane0_wait(bar_done + 8 * s, ph ^ 1u, abort_word, kAbortActEmpty, lane)) { ok = false; break; }
+                    const uint32_t s = it % NB;
+                    const uint32_t last = it * KS + (KS - 1);
+                    if (last >= static_cast<uint32_t>(NBS)) {
+                        const uint32_t jw = (last - NBS) / KS;
+                        if (!lane0_wait(bar_done + 8 * (jw % NB), (jw / NB) & 1u, abort_word, kAbortActEmpty, lane)) { ok = false; break; }
+                    }
                     for (int ks = 0; ks < KS; ++ks) {
                         const int step = stage * KS + ks;
                         int set = MODE == kFwd ? 0 : step / steps_set;
                         int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
                         if (step >= nsteps) { set = 0; red0 = red_total; }   // a step past the end: zeros
                         const __nv_bfloat16* src = args.act[set];
-                        uint8_t* dst = act_g + s * kActStageBytes + ks * kActTileBytes;
+                        uint8_t* dst = act_g + ((it * KS + ks) % NBS) * kActTileBytes;
                         const int my_rows = t.ntok_pad / CG;
                         for (int idx = lane; idx < my_rows * 8; idx += 32) {
                             const int r = idx >> 3, c = idx & 7;
@@ -413,7 +423,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             // the peer's copies of the barriers the commits signal
             const uint32_t peer_done = CG == 2 ? map_to_cta(bar_done, 1) : 0u;
             const uint32_t peer_acc_full = CG == 2 ? map_to_cta(bar_acc_full, 1) : 0u;
-            uint32_t a_lo = a_lo0, b_lo = b_lo0, sa = 0, sb = 0, ph = 0;
+            uint32_t sa = 0, sb = 0, sbar = 0, ph = 0;   // next decoded-weight slot, activation slot, barrier pair
             uint32_t full_bar = bar_full, done_bar = bar_done;
             uint32_t tl = 0;
             bool ok = true, ready = false;
@@ -429,20 +439,24 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     umma_idesc_bf16(static_cast<uint32_t>(t.ntok_pad), MODE == kBwd ? 1u : 0u, 0u, 128u * CG);
                 for (int stage = 0; stage < nstages; ++stage) {
                     if (!ready && !mbar_wait(full_bar, ph, abort_word, kAbortWgtFull)) { ok = false; break; }
-                    const uint32_t cur_done = done_bar, cur_a = a_lo, cur_b = b_lo;
-                    // advance the rings (independent of the UMMAs below, so it overlaps their issue)
-                    a_lo += kWgtStageBytes >> 4;
-                    if (++sa == NA) { sa = 0; a_lo = a_lo0; }
-                    b_lo += kActStageBytes >> 4;
+                    const uint32_t cur_done = done_bar;
+                    uint32_t slot_a[KS], slot_b[KS];
+#pragma unroll
+                    for (int ks = 0; ks < KS; ++ks) {
+                        slot_a[ks] = a_lo0 + sa * (kWgtTileBytes >> 4);
+                        slot_b[ks] = b_lo0 + sb * (kActTileBytes >> 4);
+                        if (++sa == NAS) sa = 0;
+                        if (++sb == NBS) sb = 0;
+                    }
                     full_bar += 8;
                     done_bar += 8;
-                    if (++sb == NB) { sb = 0; b_lo = b_lo0; full_bar = bar_full; done_bar = bar_done; ph ^= 1u; }
+                    if (++sbar == NB) { sbar = 0; full_bar = bar_full; done_bar = bar_done; ph ^= 1u; }
                     // with short stages, test the next stage's barrier now: the answer arrives while
                     // the UMMAs issue; "no" only means "ask again, blocking"
                     ready = KS == 1 ? mbar_try_wait(full_bar, ph) : false;
 #pragma unroll
                     for (uint32_t ks = 0; ks < static_cast<uint32_t>(KS); ++ks) {
-                        const uint32_t sa_lo = cur_a + ks * (kWgtTileBytes >> 4), sb_lo = cur_b + ks * (kActTileBytes >> 4);
+                        const uint32_t sa_lo = slot_a[ks], sb_lo = slot_b[ks];
 #pragma unroll
                         for (uint32_t kk = 0; kk < kStepK / 16; ++kk) {
                             const uint32_t accum = (ks | kk) != 0 ? 1u : (stage != 0 ? 1u : 0u);
@@ -538,11 +552,11 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         uint32_t raw_it = 0;   // forward: raw stages consumed; backward: running step index at the tile start
         bool ok = true;
 
-        // waits until decoded-weight stage (it % NA) is free, decodes into it and signals the step
+        // waits until decoded-weight slot (it % NAS) is free, decodes into it and signals the step
         auto emit = [&](uint32_t blk, int g, bool valid, uint32_t raw_bar_to_release) -> bool {
-            const uint32_t stg = it / KS, ks = it % KS;   // pipeline stage (running index) and step inside it
-            if (stg >= static_cast<uint32_t>(NA)) {
-                const uint32_t j = stg - NA;  // the stage that last used this slot
+            const uint32_t stg = it / KS;   // pipeline stage (running index) of this step
+            if (it >= static_cast<uint32_t>(NAS)) {
+                const uint32_t j = (it - NAS) / KS;  // the stage of the step that last used this slot
                 if (!all_wait(bar_done + 8 * (j % NB), (j / NB) & 1u, abort_word, kAbortWgtEmpty)) return false;
             }
             uint4 o[4];
@@ -551,7 +565,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             } else {
                 o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
             }
-            const uint32_t tile_s = wgt_s + (stg % NA) * kWgtStageBytes + ks * kWgtTileBytes;
+            const uint32_t tile_s = wgt_s + (it % NAS) * kWgtTileBytes;
 #pragma unroll
             for (int c = 0; c < 4; ++c) sts128(tile_s + coff[c], o[c]);
             fence_proxy_async_smem();
