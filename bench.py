@@ -485,7 +485,7 @@ def gpu_arm(args):
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the GEMM kernel on this
 # workload, from the ncu capture summarised under profiles/; None until a capture exists.
-MEASURED_DRAM_TRAFFIC = {"fwd": 477.5e6, "bwd": 441.8e6}  # profiles/mmq_gemm_q4k_grouped_ncu_full.txt
+MEASURED_DRAM_TRAFFIC = {"fwd": 477.2e6, "bwd": 442.8e6}  # profiles/mmq_gemm_q4k_grouped_ncu_full.txt
 
 
 def reference_arm(args):
