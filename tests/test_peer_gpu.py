@@ -12,7 +12,7 @@ from helpers import DX_TOL, FWD_TOL, bits, to_dev
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_virtual_ranks_dispatch_matmul_pull(cuda, world):
     from torch_ggml_ops_b200 import native
 
