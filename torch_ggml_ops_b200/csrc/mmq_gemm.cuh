@@ -96,7 +96,6 @@ constexpr int kTmemCols = 512;       // two accumulators of 256 columns
 constexpr int kNumBoxes = 5;         // activation TMA boxes of 256, 128, 64, 32, 16 rows
 constexpr int kSmemLimit = 232448;   // 227 KB opt-in limit per CTA
 constexpr int kEpiStageBytes = kEpilogueWarps * 16 * 64;  // per epilogue warp: 16 tokens x 32 outputs, bf16
-constexpr int kTaskCache = 64;       // token-tile records of the CTA's first tiles kept in shared memory
 
 struct ActMaps {
     CUtensorMap box[kNumBoxes];
@@ -161,7 +160,6 @@ struct GemmCfg {
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kGridBytes = QT == QT_IQ2_S ? 8192 : 0;
     static constexpr int kFixed = 1024 /*alignment slack*/ + 512 /*barriers etc.*/ + 128 /*read slack*/ + kEpiStageBytes +
-                                  kTaskCache * 16 /*tile records*/ +
                                   kActSlots * kActTileBytes + kRawBytes + kGridBytes;
     static constexpr int kWgtSlotsFit = (kSmemLimit - kFixed) / kWgtTileBytes;
     static constexpr int kWgtSlots = kWgtSlotsFit >= kWgtSlotsMax ? kWgtSlotsMax : kWgtSlotsFit;
@@ -177,15 +175,13 @@ struct TileInfo {
 
 
 // `mtiles` / `mtiles_set` count tiles of CG * 128 weight rows; `rank` is the CTA's rank in its pair.
-// `cache` holds the records of this CTA's first kTaskCache tiles (index `nth`): a record read
-// from global memory costs every role a round trip to L2 at each tile boundary.
 template <int MODE, int CG>
 __device__ __forceinline__ bool load_tile(const GemmArgs& a, int tile, int mtiles, int mtiles_set,
-                                          int rank, const int4* cache, int nth, TileInfo& t) {
+                                          int rank, TileInfo& t) {
     const int task = tile / mtiles;
     const int mt = tile - task * mtiles;
     if (a.tasks != nullptr) {
-        const int4 k = nth < kTaskCache ? cache[nth] : a.tasks[task];
+        const int4 k = a.tasks[task];
         t.expert = k.x;
         t.row0 = k.y;
         t.ntok = k.z;
@@ -261,7 +257,6 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     const uint32_t bar_acc_empty = bar_acc_full + 16;        // 2
     constexpr int kBarBytes = 8 * (2 * NB + 2 * NR + 4);
     static_assert(kBarBytes + 16 <= 512, "misc region");
-    const int4* task_cache = reinterpret_cast<const int4*>(misc_g + 512);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc_g + kBarBytes);
     volatile int* abort_word = reinterpret_cast<volatile int*>(misc_g + kBarBytes + 4);
 
@@ -295,13 +290,6 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         *abort_word = 0;
         mbar_fence_init();
     }
-    if (args.tasks != nullptr) {
-        int4* dst = reinterpret_cast<int4*>(misc_g + 512);
-        for (int i = threadIdx.x; i < kTaskCache; i += kGemmThreads) {
-            const long long tile = cta + static_cast<long long>(i) * ncta;
-            if (tile < total_tiles) dst[i] = args.tasks[tile / mtiles];
-        }
-    }
     if (QT == QT_IQ2_S) {
         uint64_t* gdst = reinterpret_cast<uint64_t*>(grid_g);
         for (int i = threadIdx.x; i < 1024; i += kGemmThreads) gdst[i] = args.iq2s_grid[i];
@@ -331,10 +319,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     for (int b = 0; b < kNumBoxes; ++b) prefetch_tmap(&args.act_maps[s].box[b]);
                 uint32_t it = 0;
                 bool ok = true;
-                int nth = 0;
-            for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
+                for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                     TileInfo t;
-                    if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, task_cache, nth++, t)) continue;
+                    if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                     for (int stage = 0; stage < nstages; ++stage, ++it) {
                         const uint32_t s = it % NB;
                         // the stage's last step reuses the slot of step (last - NBS): wait for that stage's UMMAs
@@ -379,10 +366,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             uint32_t it = 0;
             bool ok = true;
             const int red_total = MODE == kFwd ? K : N;
-            int nth = 0;
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, task_cache, nth++, t)) continue;
+                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 for (int stage = 0; stage < nstages; ++stage, ++it) {
                     const uint32_t s = it % NB;
                     const uint32_t last = it * KS + (KS - 1);
@@ -441,10 +427,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             uint32_t full_bar = bar_full, done_bar = bar_done;
             uint32_t tl = 0;
             bool ok = true, ready = false;
-            int nth = 0;
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, task_cache, nth++, t)) continue;
+                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
                 ++tl;
                 if (!mbar_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kAbortAccEmpty)) break;
@@ -506,10 +491,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             constexpr int kRows = Cfg::kRawRows;
             for (int s = 0; s < args.nsets; ++s)
                 for (int c = 0; c < P; ++c) prefetch_tmap(&args.wgt_maps[s].cls[c]);
-            int nth = 0;
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, task_cache, nth++, t)) continue;
+                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 const int nraw = MODE == kFwd ? nkb : nsteps_pad;
                 for (int ri = 0; ri < nraw; ++ri, ++itr) {
                     const uint32_t r = itr % NR, ph = (itr / NR) & 1u;
@@ -594,10 +578,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             return true;
         };
 
-        int nth = 0;
-            for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
+        for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
             TileInfo t;
-            if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, task_cache, nth++, t)) continue;
+            if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
             const long long gexp = static_cast<long long>(t.expert) * N;
             if (MODE == kFwd) {
                 const bool row_ok = t.m0 + row < N;
@@ -649,10 +632,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         const int ehalf = (warp - kFirstEpilogueWarp) >> 2;     // which of the alternate 16-token chunks
         uint32_t tl = 0;
         const int mdim = MODE == kFwd ? N : K;
-        int nth = 0;
         for (long long tile = cta; tile < total_tiles; tile += ncta) {
             TileInfo t;
-            if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, task_cache, nth++, t)) continue;
+            if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
             const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
             ++tl;
             if (!all_wait(bar_acc_full + 8 * acc, aph, abort_word, kAbortAccFull)) break;
