@@ -454,7 +454,12 @@ def gpu_arm(args):
         e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
         h2d = xh.numel() * 2 + dyh.numel() * 2
         d2h = yh.numel() * 2 + dxh.numel() * 2
-        launches = 4 + (3 + 2 + 4 if pep is not None else 3 + 6)  # GEMMs + tile builders, routing sort, plan, exchange kernels
+        # this library's kernels per step: GEMMs + tile builders (4), routing sort (3), plan (2, + 1 for the
+        # token maps), exchange (pair level 4; token level 6: dispatch, expand, pull y, dispatch dy, reduce, pull)
+        if pep is None:
+            launches = 4 + 3 + 6
+        else:
+            launches = (4 + 3 + (3 + 6 if args.token_level else 2 + 4)) * max(1, args.micro)
         result["device_status"] = native.device_status()
         if pep is not None:
             result["ep_overflow"] = int(sum(int(q.overflow.item()) for q in peps))
