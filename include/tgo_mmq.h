@@ -55,9 +55,20 @@ const char* tgo_last_error(void);
 int64_t tgo_block_bytes(int quant_type);
 
 /* Reads (synchronously) and clears the device status word that kernels set when a bounded wait
- * gives up.  *status = 0 means no kernel ever gave up.  No counterpart in the reference (its
- * kernels have no inter-warp waits). */
+ * gives up: *status = code | block << 8, 0 means no kernel gave up since the last read.  A kernel
+ * that gave up returns with its outputs incomplete, and the asynchronous calls cannot report that
+ * themselves: poll this where the host synchronises anyway (end of a step), or set the environment
+ * variable TGO_CHECK_STATUS=1, which makes every matmul call wait for its stream and return
+ * TGO_E_DEVICE if the word is set (a debugging aid: it serialises host and device).  No
+ * counterpart in the reference (its kernels have no inter-warp waits). */
 int tgo_device_status(int* status);
+
+/* Test hook for the time-out path of the kernels' bounded waits: launches a one-block kernel in
+ * which a warp waits, for at most limit_cycles SM cycles (1000..200000000), on a barrier nobody
+ * arrives on.  The wait gives up and the kernel records code 10 in the status word, which
+ * tgo_device_status then returns (and clears).  Nothing else is in flight in that kernel, the
+ * context stays usable.  No counterpart in the reference. */
+int tgo_selftest_wait_timeout(int64_t limit_cycles, void* stream);
 
 /* Decode n_blocks consecutive super-blocks to bf16 (round-to-nearest-even), 256 values each.
  * The same device decoders feed the matmul kernels; exposed for bit-exact checks against
@@ -81,12 +92,16 @@ int tgo_mmq_dx(const void* dy, const void* packed_weight, void* dx, int64_t rows
  * csrc/mmq_hip.cu:544-558). */
 int64_t tgo_grouped_workspace_bytes(int64_t rows, int64_t num_groups);
 
-/* Builds the tile list (device prefix sum over the groups) into `workspace`.  The grouped calls
- * below do this themselves; exposed for tests.  Replaces grouped_mmq_build_row_tasks
- * (csrc/mmq_core.cuh:516-571). */
+/* Builds the tile list (device prefix sum over the groups) into `workspace`: int32 count at byte
+ * 0, then from byte 16 one int32x4 (expert, first row, tokens, group) per tile; a group is cut
+ * into ceil(size / max_tile_tokens) tiles of equal size rounded up to 16.  max_tile_tokens is
+ * 256 or 512 (a tile of more than 256 tokens uses both accumulators of the matmul kernel and
+ * shares each decoded weight step between them).  The grouped calls below do this themselves;
+ * exposed for tests.  Replaces grouped_mmq_build_row_tasks (csrc/mmq_core.cuh:516-571). */
 int tgo_build_tiles(const int64_t* expert_indices, const int32_t* expert_offsets,
-                    int64_t num_groups, int64_t num_experts, int64_t rows, void* workspace,
-                    int64_t workspace_bytes, void* stream);
+                    int64_t num_groups, int64_t num_experts, int64_t rows,
+                    int64_t max_tile_tokens, void* workspace, int64_t workspace_bytes,
+                    void* stream);
 
 /* Grouped forward over expert-sorted rows; with w1/y1 non-null also the second projection of a
  * gate/up pair from the same activations (y0 = X*W0[e]^T, y1 = X*W1[e]^T).
@@ -128,9 +143,10 @@ int tgo_route_sort(const int32_t* expert_ids, int64_t n_pairs, int64_t num_exper
                    int64_t workspace_bytes, void* stream);
 
 /* dst[r][:] = src[index[r] / divisor][:] for bf16 rows of `width` (a multiple of 8); with
- * index = sorted_to_pair and divisor = top_k this builds the expert-sorted activation rows. */
-int tgo_gather_rows(const void* src, const int32_t* index, int64_t divisor, void* dst,
-                    int64_t n_rows, int64_t width, void* stream);
+ * index = sorted_to_pair and divisor = top_k this builds the expert-sorted activation rows.  An
+ * index that is negative, or whose source row is not below src_rows, gives a row of zeros. */
+int tgo_gather_rows(const void* src, int64_t src_rows, const int32_t* index, int64_t divisor,
+                    void* dst, int64_t n_rows, int64_t width, void* stream);
 
 /* out[t][:] = sum over slots of weights[t][slot] * rows[pair_to_sorted[t*top_k+slot]][:] (fp32
  * accumulation, one bf16 rounding; weights may be null = 1). */
@@ -188,7 +204,8 @@ int tgo_ep_pull(void* const* peer_ptrs, int64_t world, const int32_t* dst_rank, 
  *                         and, on the pair's owner, row_slot[owner][row] = slot (int32 [capacity]);
  *  tgo_ep_dispatch_tokens writes src[t] into the token buffer of every GPU that owns one of t's experts;
  *  tgo_ep_expand          owner side: rows[row] = token_buffer[row_slot[row]] for row < *n_rows_device
- *                         (a device int32, e.g. the last cumulative offset of tgo_ep_plan);
+ *                         (a device int32, e.g. the last cumulative offset of tgo_ep_plan); a row whose
+ *                         entry is outside [0, n_slots) is left untouched;
  *  tgo_ep_reduce          owner side: partial_sums[slot] = sum of rows[slot_rows[slot][s]] (fp32, one rounding);
  *  tgo_ep_pull_tokens     out[t] = sum over the GPUs owning one of t's experts of their partial_sums[slot]. */
 int tgo_ep_token_maps(const int32_t* dst_rank, const int32_t* dst_row, int64_t tokens, int64_t top_k,
@@ -197,8 +214,9 @@ int tgo_ep_token_maps(const int32_t* dst_rank, const int32_t* dst_row, int64_t t
 int tgo_ep_dispatch_tokens(const void* src, const int32_t* dst_rank, int64_t tokens, int64_t top_k,
                            int64_t width, int64_t my_rank, int64_t tokens_per_rank,
                            void* const* token_buffer_ptrs, int64_t world, void* stream);
-int tgo_ep_expand(const void* token_buffer, const int32_t* row_slot, const int32_t* n_rows_device,
-                  void* rows, int64_t capacity, int64_t width, void* stream);
+int tgo_ep_expand(const void* token_buffer, int64_t n_slots, const int32_t* row_slot,
+                  const int32_t* n_rows_device, void* rows, int64_t capacity, int64_t width,
+                  void* stream);
 int tgo_ep_reduce(const void* rows, const int32_t* slot_rows, int64_t n_slots, int64_t top_k,
                   void* partial_sums, int64_t width, void* stream);
 int tgo_ep_pull_tokens(void* const* partial_sum_ptrs, int64_t world, const int32_t* dst_rank,

@@ -215,6 +215,20 @@ def rel_frobenius(test, ref) -> float:
     return float(num / den) if float(den) > 0 else float(num)
 
 
+def max_row_error(test, ref) -> float:
+    """max over rows of ||test[r] - ref[r]|| / ||ref[r]||, over the rows whose reference is finite.
+    A norm over the whole output hides a handful of wrong rows in a large matrix; this does not."""
+    import torch
+
+    ref = ref.to(torch.float64)
+    test = test.to(torch.float64)
+    rows = torch.isfinite(ref).all(dim=1)
+    num = torch.linalg.vector_norm((test - ref)[rows], dim=1)
+    den = torch.linalg.vector_norm(ref[rows], dim=1)
+    err = torch.where(den > 0, num / den.clamp_min(1e-300), num)
+    return float(err.max()) if err.numel() else 0.0
+
+
 def quantize_q8(x):
     """q8_1-style activation blocks of 32 values (csrc/mmq_core.cuh:151-209): returns
     (int8 quants, fp32 d = amax/127, fp32 sum of the unquantised values), numpy arrays.

@@ -56,7 +56,7 @@ def test_argument_validation_happens_before_any_device_work():
          "exceeds packed expert count"),
         (lambda: lib.tgo_grouped_fwd(p, p, p, p, None, p, p, 1, 1, 4, 8, 256, 12, p, 4096, None), "both"),
         (lambda: lib.tgo_grouped_dx(p, None, p, None, p, p, p, 1, 1, 4, 8, 256, 12, p, 8, None), "workspace"),
-        (lambda: lib.tgo_build_tiles(p, p, 0, 1, 4, p, 4096, None), "at least one active expert"),
+        (lambda: lib.tgo_build_tiles(p, p, 0, 1, 4, 256, p, 4096, None), "at least one active expert"),
         (lambda: lib.tgo_dequantize_bf16(p, 0, 12, p, None), "n_blocks"),
     ]
     for call, needle in cases:

@@ -1,7 +1,8 @@
 """The GEMM kernel exists in two forms: CTA pairs (cta_group::2 UMMAs over a cluster of two, the
 default) and single CTAs (TGO_CTA_PAIR=0, also the fallback where a pair cannot be co-scheduled).
 The choice is read once per process, so the single-CTA form is exercised in a child process; both
-forms must give bit-identical results (the reduction order does not depend on the tiling).
+forms must give bit-identical results (the reduction order does not depend on the tiling), with
+256-token tiles and with 512-token tiles (TGO_WIDE_TILES).
 """
 import json
 import os
@@ -60,8 +61,8 @@ print("RESULT " + json.dumps(out))
 """
 
 
-def _run(pair: str) -> dict:
-    env = dict(os.environ, TGO_CTA_PAIR=pair)
+def _run(pair: str, wide: str) -> dict:
+    env = dict(os.environ, TGO_CTA_PAIR=pair, TGO_WIDE_TILES=wide)
     p = subprocess.run([sys.executable, "-c", CHILD, str(ROOT)], env=env, capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-4000:]
     line = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")][-1]
@@ -69,8 +70,10 @@ def _run(pair: str) -> dict:
 
 
 def test_single_cta_and_pair_kernels_agree_bit_for_bit():
-    single = _run("0")
-    pair = _run("1")
-    assert single.keys() == pair.keys()
-    for k in single:
-        assert single[k] == pair[k], k
+    """Also across tile widths: 256-token tiles and 512-token (two-accumulator) tiles."""
+    runs = {(pair, wide): _run(pair, wide) for pair in ("0", "1") for wide in ("0", "1")}
+    first = runs[("1", "0")]
+    for key, got in runs.items():
+        assert got.keys() == first.keys()
+        for k in first:
+            assert got[k] == first[k], (key, k)

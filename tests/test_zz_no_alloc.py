@@ -60,3 +60,27 @@ def test_sizes_beyond_the_built_in_scratch_are_rejected(cuda):
         native.check(native.lib().tgo_grouped_fwd_noalloc(
             buf.data_ptr(), buf.data_ptr(), None, buf.data_ptr(), None, buf.data_ptr(), buf.data_ptr(),
             1, 1, rows, 8, 256, 12, None), "tgo_grouped_fwd_noalloc")
+
+
+def test_the_limit_itself_is_accepted(cuda):
+    """rows / 256 + groups == TGO_NOALLOC_MAX_TILES exactly: 4000 one-row-tile experts (N = 8,
+    K = 256) and 24576 rows; same bits as the workspace entry point."""
+    from torch_ggml_ops_b200 import native
+
+    qt, E, N, K, R = ref.Q4_K, 4000, 8, 256, 24576
+    assert R // 256 + E == native.NOALLOC_MAX_TILES
+    rng = np.random.default_rng(5)
+    sizes = rng.multinomial(R, np.full(E, 1.0 / E)).astype(np.int64)
+    ei, eo = routing_from_sizes(sizes, range(E))
+    w = to_dev(blocks.expert_weights(qt, E, N, K, 11))
+    x = to_dev(blocks.gaussian_bf16((R, K), 12))
+    eid, eod = to_dev(ei), to_dev(eo)
+    y_a = torch.full((R, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    y_b = torch.full((R, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(native.grouped_workspace_bytes(R, E), dtype=torch.uint8, device="cuda")
+    native.grouped_fwd(x, w, None, y_a, None, eid, eod, E, R, N, K, qt, ws)
+    native.grouped_fwd_noalloc(x, w, None, y_b, None, eid, eod, E, R, N, K, qt)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(y_a), bits(y_b)) and not torch.isnan(y_b).any()
+    with pytest.raises(RuntimeError, match="exceeds the built-in limit"):
+        native.grouped_fwd_noalloc(x, w, None, y_b, None, eid, eod, E, R + 256, N, K, qt)

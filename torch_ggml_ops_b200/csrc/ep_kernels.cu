@@ -22,7 +22,8 @@ constexpr int kEpMaxRanks = 64;
 // whose buffer rows are ordered by (local expert, source rank, position in the source's sorted
 // order).  One block.
 __global__ void __launch_bounds__(1024) ep_offsets_kernel(const int32_t* __restrict__ counts, int W, int E, int EL, int me,
-                                                          int32_t* __restrict__ dst_base, int32_t* __restrict__ seg_start,
+                                                          int capacity, int32_t* __restrict__ dst_base,
+                                                          int32_t* __restrict__ seg_start,
                                                           int64_t* __restrict__ local_indices,
                                                           int32_t* __restrict__ local_offsets) {
     // per expert: rows from all sources, rows from the sources before this rank, this rank's rows
@@ -49,7 +50,9 @@ __global__ void __launch_bounds__(1024) ep_offsets_kernel(const int32_t* __restr
         seg_start[e] = mine_before;
         if (e / EL == me) {
             local_indices[e - first] = e - first;
-            local_offsets[e - first] = before_experts + total[e];
+            // rows at or beyond the capacity are dropped by ep_map_kernel (and flagged): the group
+            // that straddles the capacity keeps the rows that fit, later groups become empty
+            local_offsets[e - first] = min(before_experts + total[e], capacity);
         }
     }
 }
@@ -181,16 +184,20 @@ __global__ void __launch_bounds__(256) ep_dispatch_tokens_kernel(const uint4* __
 }
 
 // Owner side: rows[row][:] = tok[row_slot[row]][:] for the rows that exist (*n_rows, a device value).
+// A row whose slot entry is not a slot of the token buffer (nobody announced that row through
+// tgo_ep_token_maps) is left as it is.
 __global__ void __launch_bounds__(256) ep_expand_kernel(const uint4* __restrict__ tok, const int32_t* __restrict__ row_slot,
                                                         const int32_t* __restrict__ n_rows, uint4* __restrict__ rows,
-                                                        long long capacity, int vec_per_row) {
+                                                        long long capacity, long long n_slots, int vec_per_row) {
     long long n = *n_rows;
     if (n > capacity) n = capacity;
     const long long total = n * vec_per_row;
     for (long long v = blockIdx.x * 256LL + threadIdx.x; v < total; v += 256LL * gridDim.x) {
         const long long row = v / vec_per_row;
         const int c = static_cast<int>(v - row * vec_per_row);
-        rows[v] = tok[static_cast<long long>(row_slot[row]) * vec_per_row + c];
+        const long long slot = row_slot[row];
+        if (slot < 0 || slot >= n_slots) continue;
+        rows[v] = tok[slot * vec_per_row + c];
     }
 }
 
@@ -297,8 +304,8 @@ int tgo_ep_plan(const int32_t* counts_all, int64_t world, int64_t num_experts, i
         return route_fail(TGO_E_ARG, "n_pairs and capacity must be in 1..2^31-1");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int E = static_cast<int>(num_experts), W = static_cast<int>(world), EL = E / W;
-    ep_offsets_kernel<<<1, 1024, 0, s>>>(counts_all, W, E, EL, static_cast<int>(my_rank), scratch, scratch + E,
-                                         local_indices, local_offsets);
+    ep_offsets_kernel<<<1, 1024, 0, s>>>(counts_all, W, E, EL, static_cast<int>(my_rank), static_cast<int>(capacity),
+                                         scratch, scratch + E, local_indices, local_offsets);
     ep_map_kernel<<<static_cast<int>((n_pairs + 255) / 256), 256, 0, s>>>(
         expert_ids, pair_to_sorted, scratch, scratch + E, static_cast<int>(n_pairs), E, EL, static_cast<int>(capacity),
         dst_rank, dst_row, overflow);
@@ -369,15 +376,15 @@ int tgo_ep_dispatch_tokens(const void* src, const int32_t* dst_rank, int64_t tok
     return ep_launch_check("ep_dispatch_tokens_kernel launch failed");
 }
 
-int tgo_ep_expand(const void* token_buffer, const int32_t* row_slot, const int32_t* n_rows_device, void* rows,
-                  int64_t capacity, int64_t width, void* stream) {
+int tgo_ep_expand(const void* token_buffer, int64_t n_slots, const int32_t* row_slot, const int32_t* n_rows_device,
+                  void* rows, int64_t capacity, int64_t width, void* stream) {
     if (token_buffer == nullptr || row_slot == nullptr || n_rows_device == nullptr || rows == nullptr)
         return route_fail(TGO_E_ARG, "null pointer");
-    if (capacity <= 0 || width <= 0 || (width * 2) % 16 != 0)
-        return route_fail(TGO_E_ARG, "expand needs capacity > 0 and a row length that is a multiple of 8");
+    if (capacity <= 0 || n_slots <= 0 || width <= 0 || (width * 2) % 16 != 0)
+        return route_fail(TGO_E_ARG, "expand needs capacity > 0, slots > 0 and a row length that is a multiple of 8");
     const int vec = static_cast<int>(width / 8);
     ep_expand_kernel<<<ep_grid(capacity * vec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(token_buffer), row_slot, n_rows_device, static_cast<uint4*>(rows), capacity, vec);
+        static_cast<const uint4*>(token_buffer), row_slot, n_rows_device, static_cast<uint4*>(rows), capacity, n_slots, vec);
     return ep_launch_check("ep_expand_kernel launch failed");
 }
 

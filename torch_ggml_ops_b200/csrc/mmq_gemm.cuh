@@ -25,8 +25,14 @@
 // weight producer (TMA), 3 idle, 4-19 decode (two groups of 8 warps on alternate 64-element
 // steps), 20-23 epilogue (TMEM -> bf16 -> global).
 //
+// Wide tiles.  A tile of more than 256 tokens (up to 512) is split into two halves that use both
+// accumulators at once and share every decoded weight step: each decoded stage is consumed by two
+// consecutive pipeline stages (half 0 -> accumulator a, half 1 -> accumulator a ^ 1), so the
+// decode work per output element halves.  The epilogue sees the halves as two ordinary tiles.
+//
 // Synchronisation.  A stage is KS steps (1 for a single CTA, 2 for a pair: one step per decode
-// group); stages have running index j over all tiles of the CTA:
+// group); pipeline stages have running index j over all tiles of the CTA (a wide tile has two
+// pipeline stages per decoded stage):
 //   full[j % NB]  <- the activation TMA (expect_tx for the whole stage, announced by the leader)
 //                    and the decode warps of the stage's steps (of both CTAs); the UMMA issuer
 //                    waits on it once and issues the stage's 4 * KS UMMAs;
@@ -47,7 +53,8 @@ namespace tgo {
 enum : int { kFwd = 0, kBwd = 1 };
 
 constexpr int kTileM = 128;          // weight-side extent of one tile (TMEM lanes)
-constexpr int kTileTok = 256;        // most tokens per tile (TMEM columns of one accumulator)
+constexpr int kTileTok = 256;        // most tokens per accumulator (TMEM columns of one accumulator)
+constexpr int kWideTok = 2 * kTileTok;   // most tokens of a wide tile (both accumulators at once)
 constexpr int kStepK = 64;           // reduction elements per pipeline step (one swizzle row)
 constexpr int kWgtTileBytes = kTileM * 128;
 // Ring depths, in slots of one step (the barriers are per stage).  One CTA: 4 activation slots of
@@ -86,6 +93,9 @@ constexpr int kDecodeWarps = 8;        // warps of one decode group (256 threads
 constexpr int kDecodeGroups = 2;       // groups take alternate steps, so two steps decode at once
 constexpr int kFirstDecodeWarp = 4;
 constexpr int kFirstEpilogueWarp = kFirstDecodeWarp + kDecodeWarps * kDecodeGroups;  // multiple of 4
+#ifndef TGO_EPI_PREFETCH
+#define TGO_EPI_PREFETCH 1
+#endif
 #ifndef TGO_EPILOGUE_WARPS
 #define TGO_EPILOGUE_WARPS 4
 #endif
@@ -115,11 +125,8 @@ struct GemmArgs {
     ActMaps act_maps[2];                 // per set: activations [rows][red] bf16, 128B swizzle
     WgtMaps wgt_maps[2];                 // per set: packed weight rows by alignment class
     const __nv_bfloat16* act[2];         // same tensors, for the non-TMA loader
-    const uint8_t* wgt[2];               // packed weights [E][N][K/256 blocks]
     __nv_bfloat16* out[2];
-    long long expert_bytes;              // N * (K/256) * block bytes
-    long long wgt_bytes;                 // E * expert_bytes
-    const int4* tasks;                   // (expert, first row, tokens, -) or null for dense
+    const int4* tasks;                   // (expert, first row, tokens <= 512, group) or null for dense
     const int* task_count;               // device count of tasks (grouped)
     int* status;                         // device status word (0 = ok)
     const uint64_t* iq2s_grid;           // IQ2_S codebook (1024 entries) in global memory
@@ -127,9 +134,8 @@ struct GemmArgs {
     int out_features;                    // N
     int in_features;                     // K
     int nsets;                           // 1, or 2 for the gate/up pair
-    int num_experts;
     int dense_tasks;                     // dense: number of token tiles
-    int dense_tok;                       // dense: tokens per tile (multiple of 16)
+    int dense_tok;                       // dense: tokens per tile (multiple of 16, at most 512)
     int use_tma;                         // 0: activation rows are not 16-byte multiples
     int wgt_classes;                     // P: alignment classes of the packed weight rows (1, 2, 4 or 8)
     int wgt_classes_log2;
@@ -139,7 +145,7 @@ struct GemmArgs {
 // CG = 1: one CTA per tile of 128 weight rows.  CG = 2: a cluster of two CTAs works on 256 weight
 // rows and one token tile with cta_group::2 UMMAs (each CTA decodes its own 128 rows and stages
 // half of the tokens; the leader CTA issues).
-template <int QT, int MODE, int CG>
+template <int QT, int MODE, int CG, int WIDE = 1>
 struct GemmCfg {
     using Fmt = BlockFmt<QT>;
     static constexpr int kSub = CG == 2 ? TGO_PAIR_SUBSTEPS : TGO_SUBSTEPS;   // steps per stage
@@ -148,14 +154,26 @@ struct GemmCfg {
     static constexpr int kActTileBytes = kActRows * 128;        // one step of activations
     static constexpr int kActSlots = CG == 2 ? TGO_PAIR_ACT_SLOTS : TGO_ACT_STAGES;          // steps of activations in flight
     static constexpr int kWgtSlotsMax = CG == 2 ? TGO_PAIR_WGT_SLOTS_MAX : TGO_WGT_STAGES_MAX;   // decoded steps in flight
-    static constexpr int kBars = 4;   // full / done barrier pairs (one per stage in flight)
+    // full / done barrier pairs.  A barrier is reused every kBars pipeline stages; whoever waits
+    // for stage q does so before stage q + kBars can complete, and whoever arrives for stage p
+    // knows that stage p - kBars has completed.  The longest such distances occur in wide tiles
+    // (a decoded slot is refilled up to 5 pipeline stages after its last reader, and the decode
+    // warps arrive for two consecutive stages), which is why there are 8 and not 4.
+    static constexpr int kBars = WIDE ? 8 : 4;
     static constexpr int kTokPad = CG == 2 ? 32 : 16;           // token padding of a tile (UMMA N granularity)
     static constexpr int kRawRows = MODE == kFwd ? 128 : 64;    // block windows per raw stage
-    // pair: as many raw stages as fit in about 56 KB (the raw ring has to cover an HBM round trip)
-    static constexpr int kRawFit = 57344 / (kRawRows * Fmt::kBox);
+    // pair: as many raw stages as fit in 60 KB (the raw ring has to cover an HBM round trip).
+    // Backward, a raw stage is one step and the two decode groups take alternate steps: the ring
+    // depth must be even, so that a stage always goes to the same group.  With an odd depth a group
+    // could reach a stage one phase ahead of its barrier - before the other group's earlier load
+    // into that stage has landed, when loads complete out of order - and a wait on a barrier that
+    // is a whole phase behind passes at once.
+    static constexpr int kRawFit = 61440 / (kRawRows * Fmt::kBox);
     static constexpr int kRawMaxPair = MODE == kFwd ? TGO_PAIR_RAW_STAGES_FWD : TGO_PAIR_RAW_STAGES_BWD;
-    static constexpr int kRawStages = CG == 2 ? (kRawFit >= kRawMaxPair ? kRawMaxPair : (kRawFit < 2 ? 2 : kRawFit))
+    static constexpr int kRawWanted = kRawFit >= kRawMaxPair ? kRawMaxPair : (kRawFit < 2 ? 2 : kRawFit);
+    static constexpr int kRawStages = CG == 2 ? (MODE == kBwd ? (kRawWanted & ~1) : kRawWanted)
                                               : (MODE == kFwd ? 2 : 4);
+    static_assert(MODE == kFwd || kRawStages % kDecodeGroups == 0, "backward raw ring depth must be a multiple of the decode groups");
     static constexpr int kRawStageBytes = kRawRows * Fmt::kBox;
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kGridBytes = QT == QT_IQ2_S ? 8192 : 0;
@@ -166,16 +184,30 @@ struct GemmCfg {
     static_assert(kWgtSlots > kSub && kActSlots > kSub, "shared memory budget: more than one stage must fit");
     // a barrier is reused every kBars stages: nobody may still wait on its previous phase then
     static_assert((kWgtSlots + kSub - 1) / kSub <= kBars && (kActSlots + kSub - 1) / kSub <= kBars, "ring deeper than the barriers");
+    // wide tiles: a decode group arrives for two pipeline stages per decoded stage, knowing only
+    // that the last reader of the slot's previous step is done, up to 2 * ceil(slots / steps per
+    // stage) - 1 pipeline stages back; the barrier it arrives on must not still be in the phase of
+    // a stage older than that
+    static_assert(!WIDE || 2 * ((kWgtSlots + kSub - 1) / kSub) <= kBars, "decoded-weight ring too deep for the barrier ring with wide tiles");
     static constexpr int kSmemBytes = kFixed + kWgtSlots * kWgtTileBytes;
 };
 
 struct TileInfo {
-    int expert, row0, ntok, ntok_pad, set, m0;
+    int expert, row0, ntok, set, m0;
+    int nhalf;   // 1, or 2 for a wide tile (more than kTileTok tokens)
+    int tok0;    // tokens of half 0; half 1 holds the other ntok - tok0
 };
 
+template <int CG>
+__device__ __forceinline__ int pad_tokens(int n) {
+    constexpr int kPad = CG == 2 ? 32 : 16;   // UMMA N granularity
+    return (n + kPad - 1) & ~(kPad - 1);
+}
+__device__ __forceinline__ int half_tokens(const TileInfo& t, int half) { return half == 0 ? t.tok0 : t.ntok - t.tok0; }
+__device__ __forceinline__ int half_row0(const TileInfo& t, int half) { return half == 0 ? t.row0 : t.row0 + t.tok0; }
 
 // `mtiles` / `mtiles_set` count tiles of CG * 128 weight rows; `rank` is the CTA's rank in its pair.
-template <int MODE, int CG>
+template <int MODE, int CG, int WIDE>
 __device__ __forceinline__ bool load_tile(const GemmArgs& a, int tile, int mtiles, int mtiles_set,
                                           int rank, TileInfo& t) {
     const int task = tile / mtiles;
@@ -184,14 +216,19 @@ __device__ __forceinline__ bool load_tile(const GemmArgs& a, int tile, int mtile
         const int4 k = a.tasks[task];
         t.expert = k.x;
         t.row0 = k.y;
-        t.ntok = k.z;
+        t.ntok = min(k.z, WIDE ? kWideTok : kTileTok);
     } else {
         t.expert = 0;
         t.row0 = task * a.dense_tok;
         t.ntok = min(a.dense_tok, a.rows - t.row0);
     }
-    constexpr int kPad = CG == 2 ? 32 : 16;
-    t.ntok_pad = (t.ntok + kPad - 1) & ~(kPad - 1);
+    if (WIDE && t.ntok > kTileTok) {
+        t.nhalf = 2;
+        t.tok0 = pad_tokens<CG>((t.ntok + 1) >> 1);
+    } else {
+        t.nhalf = 1;
+        t.tok0 = t.ntok;
+    }
     if (MODE == kFwd) {
         t.set = mt / mtiles_set;
         t.m0 = ((mt - t.set * mtiles_set) * CG + rank) * kTileM;
@@ -219,10 +256,12 @@ __device__ __forceinline__ bool all_wait(uint32_t bar, uint32_t parity, volatile
     return __all_sync(0xFFFFFFFFu, ok) != 0;
 }
 
-template <int QT, int MODE, int CG>
+// WIDE = 0: every tile has at most 256 tokens and one accumulator (the wide-tile paths compile
+// out); WIDE = 1: tiles of up to 512 tokens.
+template <int QT, int MODE, int CG, int WIDE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
-    using Cfg = GemmCfg<QT, MODE, CG>;
+    using Cfg = GemmCfg<QT, MODE, CG, WIDE>;
     using Fmt = BlockFmt<QT>;
     // NAS / NBS: decoded-weight and activation slots (one step each); NB: stage barriers
     constexpr int NAS = Cfg::kWgtSlots, NBS = Cfg::kActSlots, NB = Cfg::kBars, NR = Cfg::kRawStages;
@@ -270,7 +309,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     const int mtiles = MODE == kFwd ? mtiles_set * args.nsets : mtiles_set;
     const int steps_set = MODE == kFwd ? K / kStepK : (N + kStepK - 1) / kStepK;
     const int nsteps = MODE == kFwd ? steps_set : steps_set * args.nsets;   // 64-element steps of a tile
-    const int nstages = (nsteps + KS - 1) / KS;                              // pipeline stages of a tile
+    const int nstages = (nsteps + KS - 1) / KS;                              // decoded stages of a tile
     const int nsteps_pad = nstages * KS;   // a stage's missing steps are fed zeros
     const int ntasks = args.tasks != nullptr ? *args.task_count : args.dense_tasks;
     const long long total_tiles = static_cast<long long>(ntasks) * mtiles;
@@ -313,6 +352,8 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
 
     if (warp == 0) {
         // ------------------------------------------------------------ activation producer
+        // One pipeline stage = KS one-step slots of the tokens of one half.  `it` is the running
+        // pipeline-stage index; stage it uses slots it * KS .. it * KS + KS - 1 (mod NBS).
         if (args.use_tma) {
             if (lane == 0) {
                 for (int s = 0; s < args.nsets; ++s)
@@ -321,8 +362,12 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 bool ok = true;
                 for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                     TileInfo t;
-                    if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
-                    for (int stage = 0; stage < nstages; ++stage, ++it) {
+                    if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+                    const int npipe = nstages * t.nhalf;
+                    for (int ps = 0; ps < npipe; ++ps, ++it) {
+                        const int stage = t.nhalf == 2 ? ps >> 1 : ps;
+                        const int half = t.nhalf == 2 ? ps & 1 : 0;
+                        const int hpad = pad_tokens<CG>(half_tokens(t, half));
                         const uint32_t s = it % NB;
                         // the stage's last step reuses the slot of step (last - NBS): wait for that stage's UMMAs
                         const uint32_t last = it * KS + (KS - 1);
@@ -334,7 +379,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                         // of the token rows (all of them, or its half) and the bytes count on the
                         // leader's barrier
                         const uint32_t bar = lead_full + 8 * s;
-                        if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, static_cast<uint32_t>(t.ntok_pad) * 128u * KS);
+                        if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, static_cast<uint32_t>(hpad) * 128u * KS);
 #pragma unroll
                         for (int ks = 0; ks < KS; ++ks) {
                             const int step = stage * KS + ks;
@@ -343,8 +388,8 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                             int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
                             if (step >= nsteps) { set = 0; red0 = (steps_set + (step - nsteps)) * kStepK; }
                             uint32_t dst = act_s + ((it * KS + ks) % NBS) * kActTileBytes;
-                            int rem = t.ntok_pad / CG;
-                            int row = t.row0 + rank * rem;
+                            int rem = hpad / CG;
+                            int row = half_row0(t, half) + rank * rem;
 #pragma unroll
                             for (int b = 0; b < kNumBoxes; ++b) {
                                 const int h = 256 >> b;
@@ -368,8 +413,13 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             const int red_total = MODE == kFwd ? K : N;
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
-                for (int stage = 0; stage < nstages; ++stage, ++it) {
+                if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+                const int npipe = nstages * t.nhalf;
+                for (int ps = 0; ps < npipe; ++ps, ++it) {
+                    const int stage = t.nhalf == 2 ? ps >> 1 : ps;
+                    const int half = t.nhalf == 2 ? ps & 1 : 0;
+                    const int my_rows = pad_tokens<CG>(half_tokens(t, half)) / CG;
+                    const long long first_row = static_cast<long long>(half_row0(t, half)) + rank * my_rows;
                     const uint32_t s = it % NB;
                     const uint32_t last = it * KS + (KS - 1);
                     if (last >= static_cast<uint32_t>(NBS)) {
@@ -383,10 +433,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                         if (step >= nsteps) { set = 0; red0 = red_total; }   // a step past the end: zeros
                         const __nv_bfloat16* src = args.act[set];
                         uint8_t* dst = act_g + ((it * KS + ks) % NBS) * kActTileBytes;
-                        const int my_rows = t.ntok_pad / CG;
                         for (int idx = lane; idx < my_rows * 8; idx += 32) {
                             const int r = idx >> 3, c = idx & 7;
-                            const long long grow = static_cast<long long>(t.row0) + rank * my_rows + r;
+                            const long long grow = first_row + r;
                             alignas(16) __nv_bfloat16 v[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) {
@@ -408,9 +457,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ UMMA issuer (one thread)
-        // This thread's instruction stream is the serial spine of the kernel: per stage it waits
-        // once, issues 4 * KS UMMAs and commits once (twice for a pair); every one of these costs
-        // it 50-70 cycles whatever the UMMA's size.  The loop keeps stage counters, barrier
+        // This thread's instruction stream is the serial spine of the kernel: per pipeline stage it
+        // waits once, issues 4 * KS UMMAs and commits once (twice for a pair); every one of these
+        // costs it 50-70 cycles whatever the UMMA's size.  The loop keeps stage counters, barrier
         // addresses and the low descriptor words as running values (one add per use).
         if (lane == 0 && rank == 0) {
             constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version, SWIZZLE_128B
@@ -425,29 +474,44 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             const uint32_t peer_acc_full = CG == 2 ? map_to_cta(bar_acc_full, 1) : 0u;
             uint32_t sa = 0, sb = 0, sbar = 0, ph = 0;   // next decoded-weight slot, activation slot, barrier pair
             uint32_t full_bar = bar_full, done_bar = bar_done;
-            uint32_t tl = 0;
+            uint32_t tl = 0;   // running accumulator use (a wide tile takes two)
             bool ok = true, ready = false;
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
-                const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
-                ++tl;
-                if (!mbar_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kAbortAccEmpty)) break;
-                tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + acc * kTileTok;
-                const uint32_t idesc =
-                    umma_idesc_bf16(static_cast<uint32_t>(t.ntok_pad), MODE == kBwd ? 1u : 0u, 0u, 128u * CG);
-                for (int stage = 0; stage < nstages; ++stage) {
+                if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+                const int npipe = nstages * t.nhalf;
+                const uint32_t hmask = t.nhalf == 2 ? 1u : 0u;
+                // per half: accumulator address and instruction descriptor (token count)
+                uint32_t d_tmem_h[2], idesc_h[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    d_tmem_h[h] = tmem_base + ((tl + h) & 1u) * kTileTok;
+                    idesc_h[h] = umma_idesc_bf16(static_cast<uint32_t>(pad_tokens<CG>(half_tokens(t, h))),
+                                                 MODE == kBwd ? 1u : 0u, 0u, 128u * CG);
+                }
+                for (int ps = 0; ps < npipe; ++ps) {
+                    const uint32_t half = static_cast<uint32_t>(ps) & hmask;
+                    const uint32_t use = tl + half, acc = use & 1u;
+                    const bool first_stage = ps < t.nhalf, last_stage = ps >= npipe - t.nhalf;
+                    if (first_stage) {   // first use of this half's accumulator: the epilogue must have drained it
+                        if (!mbar_wait(bar_acc_empty + 8 * acc, ((use >> 1) & 1u) ^ 1u, abort_word, kAbortAccEmpty)) { ok = false; break; }
+                        tc_fence_after_sync();
+                    }
+                    const uint32_t d_tmem = half ? d_tmem_h[1] : d_tmem_h[0];
+                    const uint32_t idesc = half ? idesc_h[1] : idesc_h[0];
                     if (!ready && !mbar_wait(full_bar, ph, abort_word, kAbortWgtFull)) { ok = false; break; }
                     const uint32_t cur_done = done_bar;
                     uint32_t slot_a[KS], slot_b[KS];
+                    uint32_t sa_next = sa;
 #pragma unroll
                     for (int ks = 0; ks < KS; ++ks) {
-                        slot_a[ks] = a_lo0 + sa * (kWgtTileBytes >> 4);
+                        slot_a[ks] = a_lo0 + sa_next * (kWgtTileBytes >> 4);
                         slot_b[ks] = b_lo0 + sb * (kActTileBytes >> 4);
-                        if (++sa == NAS) sa = 0;
+                        if (++sa_next == NAS) sa_next = 0;
                         if (++sb == NBS) sb = 0;
                     }
+                    // the decoded steps stay in place until the last half has read them
+                    if (half == hmask) sa = sa_next;
                     full_bar += 8;
                     done_bar += 8;
                     if (++sbar == NB) { sbar = 0; full_bar = bar_full; done_bar = bar_done; ph ^= 1u; }
@@ -459,7 +523,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                         const uint32_t sa_lo = slot_a[ks], sb_lo = slot_b[ks];
 #pragma unroll
                         for (uint32_t kk = 0; kk < kStepK / 16; ++kk) {
-                            const uint32_t accum = (ks | kk) != 0 ? 1u : (stage != 0 ? 1u : 0u);
+                            const uint32_t accum = (ks | kk) != 0 ? 1u : (first_stage ? 0u : 1u);
                             if (CG == 2) umma_bf16_lohi_pair(d_tmem, sa_lo + kk * kStepA, sb_lo + kk * kStepB, kDescHi, idesc, accum);
                             else umma_bf16_lohi(d_tmem, sa_lo + kk * kStepA, sb_lo + kk * kStepB, kDescHi, idesc, accum);
                         }
@@ -470,15 +534,16 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     } else {
                         umma_commit(cur_done);
                     }
-                }
-                if (ok) {
-                    if (CG == 2) {
-                        umma_commit_pair(bar_acc_full + 8 * acc);
-                        umma_commit_pair(peer_acc_full + 8 * acc);
-                    } else {
-                        umma_commit(bar_acc_full + 8 * acc);
+                    if (last_stage) {   // this half's accumulator is complete
+                        if (CG == 2) {
+                            umma_commit_pair(bar_acc_full + 8 * acc);
+                            umma_commit_pair(peer_acc_full + 8 * acc);
+                        } else {
+                            umma_commit(bar_acc_full + 8 * acc);
+                        }
                     }
                 }
+                tl += static_cast<uint32_t>(t.nhalf);
             }
         }
     } else if (warp == 2) {
@@ -493,7 +558,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 for (int c = 0; c < P; ++c) prefetch_tmap(&args.wgt_maps[s].cls[c]);
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+                if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 const int nraw = MODE == kFwd ? nkb : nsteps_pad;
                 for (int ri = 0; ri < nraw; ++ri, ++itr) {
                     const uint32_t r = itr % NR, ph = (itr / NR) & 1u;
@@ -548,15 +613,45 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             for (int c = 0; c < 4; ++c) coff[c] = base + (((cbase + c) ^ (row & 7)) << 4);
         }
         const int P = args.wgt_classes, lgP = args.wgt_classes_log2;
-        uint32_t it = static_cast<uint32_t>(group);  // running index of this group's next step
-        uint32_t raw_it = 0;   // forward: raw stages consumed; backward: running step index at the tile start
+        // Running state of this group.  A decoded step is read by pipeline stage `stg` (and by
+        // stg + 1 in a wide tile); its slot is free again once the last reader of the step that
+        // held it before (NAS steps earlier) has finished, stage `jw`.  Both advance by a fixed
+        // amount per step inside a tile, so they are kept as running values; only a tile's first
+        // steps, whose slot was last used by an earlier tile, look the stage up.
+        uint32_t it = static_cast<uint32_t>(group);                       // running index of this group's next step
+        uint32_t slot_off = static_cast<uint32_t>(group % NAS) * kWgtTileBytes;   // (it % NAS) * slot bytes
+        uint32_t raw_it = 0;   // forward: raw stages consumed
+        // running decoded-step and pipeline-stage indices at the start of this tile, whether it is
+        // wide, and how many pipeline stages per decoded stage the previous tile had (1 or 2)
+        uint32_t d0 = 0, p0 = 0;
+        bool wide = false;
+        uint32_t prev_per = 1;
+        uint32_t stg = 0, stg_inc = 0;
+        int jw = 0;
         bool ok = true;
+        constexpr uint32_t kSlotWrap = NAS * kWgtTileBytes;
+        constexpr int kAdv = kDecodeGroups / KS;   // decoded stages a group advances per step it decodes
 
-        // waits until decoded-weight slot (it % NAS) is free, decodes into it and signals the step
+        // last pipeline stage that reads the decoded step with running index `o` (this tile or an earlier one)
+        auto last_reader = [&](uint32_t o) -> uint32_t {
+            if (o >= d0) { const uint32_t ds = (o - d0) / KS; return wide ? p0 + 2u * ds + 1u : p0 + ds; }
+            // k steps before this tile: inside the previous tile (all tiles have nsteps_pad steps) its
+            // decoded stage counts back from that tile's end, which is p0; older steps were read
+            // before the previous tile began
+            const uint32_t k = d0 - o;
+            if (k <= static_cast<uint32_t>(nsteps_pad)) return p0 - 1u - prev_per * ((k + KS - 1) / KS - 1u);
+            return p0 - static_cast<uint32_t>(nstages) * prev_per - 1u;
+        };
+
+        // waits until this step's decoded-weight slot is free, decodes into it and signals the step
         auto emit = [&](uint32_t blk, int g, bool valid, uint32_t raw_bar_to_release) -> bool {
-            const uint32_t stg = it / KS;   // pipeline stage (running index) of this step
+            // Without wide tiles every pipeline stage is KS consecutive steps, so the stages and the
+            // slot follow from the step index alone; with them they are the running values above.
+            const uint32_t stg_now = WIDE ? stg : it / KS;
             if (it >= static_cast<uint32_t>(NAS)) {
-                const uint32_t j = (it - NAS) / KS;  // the stage of the step that last used this slot
+                uint32_t j;
+                if (WIDE) j = (it - d0 >= static_cast<uint32_t>(NAS)) ? static_cast<uint32_t>(jw) : last_reader(it - NAS);
+                else j = (it - NAS) / KS;
                 if (!all_wait(bar_done + 8 * (j % NB), (j / NB) & 1u, abort_word, kAbortWgtEmpty)) return false;
             }
             uint4 o[4];
@@ -565,22 +660,42 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             } else {
                 o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
             }
-            const uint32_t tile_s = wgt_s + (it % NAS) * kWgtTileBytes;
+            const uint32_t tile_s = wgt_s + (WIDE ? slot_off : (it % NAS) * kWgtTileBytes);
 #pragma unroll
             for (int c = 0; c < 4; ++c) sts128(tile_s + coff[c], o[c]);
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                if (CG == 2) mbar_arrive_cluster(lead_full + 8 * (stg % NB)); else mbar_arrive(bar_full + 8 * (stg % NB));
+                if (CG == 2) mbar_arrive_cluster(lead_full + 8 * (stg_now % NB)); else mbar_arrive(bar_full + 8 * (stg_now % NB));
+                if (WIDE && wide) {   // the second half reads this step in the next pipeline stage
+                    if (CG == 2) mbar_arrive_cluster(lead_full + 8 * ((stg_now + 1u) % NB)); else mbar_arrive(bar_full + 8 * ((stg_now + 1u) % NB));
+                }
                 if (raw_bar_to_release != 0) mbar_arrive(raw_bar_to_release);
             }
             it += kDecodeGroups;
+            if (WIDE) {
+                slot_off += kDecodeGroups * kWgtTileBytes;
+                if (slot_off >= kSlotWrap) slot_off -= kSlotWrap;
+                stg += stg_inc;
+                jw += static_cast<int>(stg_inc);
+            }
             return true;
         };
 
         for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
             TileInfo t;
-            if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+            if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+            wide = t.nhalf == 2;
+            if (WIDE) {
+                // this group's first step of the tile (running index parity equals the group)
+                const int first = static_cast<int>(it - d0);
+                const int per_stage = wide ? 2 : 1;          // pipeline stages per decoded stage
+                stg_inc = static_cast<uint32_t>(per_stage * kAdv);
+                stg = p0 + static_cast<uint32_t>(per_stage * (first / KS));
+                // floor((first - NAS) / KS): negative until the slot's previous step lies in this tile
+                const int ds_old = KS == 2 ? ((first - NAS) >> 1) : (first - NAS);
+                jw = static_cast<int>(p0) + per_stage * ds_old + (per_stage - 1);
+            }
             const long long gexp = static_cast<long long>(t.expert) * N;
             if (MODE == kFwd) {
                 const bool row_ok = t.m0 + row < N;
@@ -603,27 +718,28 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             } else {
                 const int g = ((t.m0 >> 7) & 1) * 4 + sub;
                 const int kb = t.m0 >> 8;
-                // this group's first step of the tile: running index parity must equal the group
-                for (int step = static_cast<int>((it - raw_it) & 0x7FFFFFFFu); step < nsteps_pad; step += kDecodeGroups) {
-                    const uint32_t ri = raw_it + step;
+                // The alignment class of a weight row repeats every P rows and a step is 64 rows,
+                // so a thread's window slot and misalignment are the same in every step of a tile.
+                int slot = row, mis = 0;
+                if (!Fmt::kAligned) {
+                    const int cls = static_cast<int>((gexp + row) & (P - 1));
+                    slot = cls * (Cfg::kRawRows >> lgP) + (row >> lgP);
+                    mis = (((cls * args.wgt_row_bytes) & 15) + kb * Fmt::kBytes) & 15;
+                }
+                const uint32_t blk0 = raw_s + slot * Fmt::kBox + mis;
+                for (int step = static_cast<int>((it - d0) & 0x7FFFFFFFu); step < nsteps_pad; step += kDecodeGroups) {
+                    const uint32_t ri = d0 + step;
                     const uint32_t r = ri % NR, rph = (ri / NR) & 1u;
                     if (!all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull)) { ok = false; break; }
-                    const int set = step >= steps_set ? 1 : 0;
-                    const int n_first = (step - set * steps_set) * kStepK;
+                    const int n_first = (step >= steps_set ? step - steps_set : step) * kStepK;
                     const bool valid = step < nsteps && n_first + row < N;
-                    uint32_t blk = 0;
-                    if (valid) {
-                        int slot = row, mis = 0;
-                        if (!Fmt::kAligned) {
-                            const int cls = static_cast<int>((gexp + n_first + row) & (P - 1));
-                            slot = cls * (Cfg::kRawRows >> lgP) + (row >> lgP);
-                            mis = (((cls * args.wgt_row_bytes) & 15) + kb * Fmt::kBytes) & 15;
-                        }
-                        blk = raw_s + r * Cfg::kRawStageBytes + slot * Fmt::kBox + mis;
-                    }
-                    if (!emit(blk, g, valid, bar_raw_empty + 8 * r)) { ok = false; break; }
+                    if (!emit(blk0 + r * Cfg::kRawStageBytes, g, valid, bar_raw_empty + 8 * r)) { ok = false; break; }
                 }
-                raw_it += nsteps_pad;
+            }
+            d0 += static_cast<uint32_t>(nsteps_pad);
+            if (WIDE) {
+                prev_per = wide ? 2u : 1u;
+                p0 += static_cast<uint32_t>(nstages * t.nhalf);
             }
         }
     } else if (warp >= kFirstEpilogueWarp) {
@@ -632,59 +748,67 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         const int ehalf = (warp - kFirstEpilogueWarp) >> 2;     // which of the alternate 16-token chunks
         uint32_t tl = 0;
         const int mdim = MODE == kFwd ? N : K;
-        for (long long tile = cta; tile < total_tiles; tile += ncta) {
+        bool ok = true;
+        for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
             TileInfo t;
-            if (!load_tile<MODE, CG>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
-            const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
-            ++tl;
-            if (!all_wait(bar_acc_full + 8 * acc, aph, abort_word, kAbortAccFull)) break;
-            tc_fence_after_sync();
-            const uint32_t taddr = tmem_base + acc * kTileTok + (static_cast<uint32_t>(quad * 32) << 16);
-            const int mq = t.m0 + quad * 32;  // first output column of this warp
-            __nv_bfloat16* out_base = args.out[MODE == kFwd ? t.set : 0] + static_cast<long long>(t.row0) * mdim;
-            if ((mdim & 7) == 0 && mq + 32 <= mdim) {
-                // Transposing path: the warp's 32 outputs x 16 tokens go through a private staging
-                // tile [token][32 outputs] so that global stores are 16 bytes per lane.
-                uint8_t* stage = epi_g + (warp - kFirstEpilogueWarp) * (16 * 64);
-                for (int c0 = 16 * ehalf; c0 < t.ntok_pad; c0 += 4 * kEpilogueWarps) {
+            if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+            for (int half = 0; half < t.nhalf; ++half, ++tl) {
+                const uint32_t acc = tl & 1u, aph = (tl >> 1) & 1u;
+                const int htok = half_tokens(t, half), hpad = pad_tokens<CG>(htok);
+                if (!all_wait(bar_acc_full + 8 * acc, aph, abort_word, kAbortAccFull)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t taddr = tmem_base + acc * kTileTok + (static_cast<uint32_t>(quad * 32) << 16);
+                const int mq = t.m0 + quad * 32;  // first output column of this warp
+                __nv_bfloat16* out_base = args.out[MODE == kFwd ? t.set : 0] + static_cast<long long>(half_row0(t, half)) * mdim;
+                if ((mdim & 7) == 0 && mq + 32 <= mdim) {
+                    // Transposing path: the warp's 32 outputs x 16 tokens go through a private staging
+                    // tile [token][32 outputs] so that global stores are 16 bytes per lane.
+                    uint8_t* stage = epi_g + (warp - kFirstEpilogueWarp) * (16 * 64);
+                    constexpr int kChunkStride = 4 * kEpilogueWarps;
                     uint32_t v[16];
-                    tmem_ld16(taddr + c0, v);
-                    tmem_ld_wait();
+                    int c0 = 16 * ehalf;
+                    if (c0 < hpad) tmem_ld16(taddr + c0, v);
+                    for (; c0 < hpad; c0 += kChunkStride) {
+                        if (!TGO_EPI_PREFETCH && c0 != 16 * ehalf) tmem_ld16(taddr + c0, v);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        *reinterpret_cast<__nv_bfloat16*>(stage + j * 64 + lane * 2) =
-                            __float2bfloat16(__uint_as_float(v[j]));
-                    __syncwarp();
+                        for (int j = 0; j < 16; ++j)
+                            *reinterpret_cast<__nv_bfloat16*>(stage + j * 64 + lane * 2) =
+                                __float2bfloat16(__uint_as_float(v[j]));
+                        // the next chunk's TMEM load runs while this one goes out to global memory
+                        if (TGO_EPI_PREFETCH && c0 + kChunkStride < hpad) tmem_ld16(taddr + c0 + kChunkStride, v);
+                        __syncwarp();
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const int r = (lane >> 2) + 8 * i, part = lane & 3;
-                        const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 64 + part * 16);
-                        if (c0 + r < t.ntok)
-                            *reinterpret_cast<uint4*>(out_base + static_cast<long long>(c0 + r) * mdim + mq + part * 8) = val;
+                        for (int i = 0; i < 2; ++i) {
+                            const int r = (lane >> 2) + 8 * i, part = lane & 3;
+                            const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 64 + part * 16);
+                            if (c0 + r < htok)
+                                *reinterpret_cast<uint4*>(out_base + static_cast<long long>(c0 + r) * mdim + mq + part * 8) = val;
+                        }
+                        __syncwarp();
                     }
-                    __syncwarp();
-                }
-            } else {
-                const int m = mq + lane;
-                const bool m_ok = m < mdim;
-                __nv_bfloat16* out = out_base + m;
-                for (int c0 = 16 * ehalf; c0 < t.ntok_pad; c0 += 4 * kEpilogueWarps) {
-                    uint32_t v[16];
-                    tmem_ld16(taddr + c0, v);
-                    tmem_ld_wait();
-                    if (m_ok) {
+                } else {
+                    const int m = mq + lane;
+                    const bool m_ok = m < mdim;
+                    __nv_bfloat16* out = out_base + m;
+                    for (int c0 = 16 * ehalf; c0 < hpad; c0 += 4 * kEpilogueWarps) {
+                        uint32_t v[16];
+                        tmem_ld16(taddr + c0, v);
+                        tmem_ld_wait();
+                        if (m_ok) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (c0 + j < t.ntok)
-                                out[static_cast<long long>(c0 + j) * mdim] = __float2bfloat16(__uint_as_float(v[j]));
+                            for (int j = 0; j < 16; ++j) {
+                                if (c0 + j < htok)
+                                    out[static_cast<long long>(c0 + j) * mdim] = __float2bfloat16(__uint_as_float(v[j]));
+                            }
                         }
                     }
                 }
-            }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                if (CG == 2) mbar_arrive_cluster(lead_acc_empty + 8 * acc); else mbar_arrive(bar_acc_empty + 8 * acc);
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (CG == 2) mbar_arrive_cluster(lead_acc_empty + 8 * acc); else mbar_arrive(bar_acc_empty + 8 * acc);
+                }
             }
         }
     }

@@ -1,6 +1,8 @@
 // One translation unit per quant type (compile with -DTGO_QT=<ggml type id>): instantiates the
 // forward and backward GEMM kernels for that type, as single-CTA kernels and as CTA-pair
 // (cluster of two) kernels, and their launch functions.
+#include <atomic>
+
 #include "mmq_launch.h"
 
 #ifndef TGO_QT
@@ -9,24 +11,25 @@
 
 namespace tgo {
 
-template <int QT, int MODE, int CG>
+template <int QT, int MODE, int CG, int WIDE>
 static cudaError_t configure() {
-    using Cfg = GemmCfg<QT, MODE, CG>;
-    static bool configured[64] = {};
+    using Cfg = GemmCfg<QT, MODE, CG, WIDE>;
+    // relaxed atomics: threads that race on a device's first call set the same attribute and flag
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev < 64 && configured[dev]) return cudaSuccess;
-    e = cudaFuncSetAttribute(mmq_gemm_kernel<QT, MODE, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (dev < 64 && configured[dev].load(std::memory_order_relaxed)) return cudaSuccess;
+    e = cudaFuncSetAttribute(mmq_gemm_kernel<QT, MODE, CG, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    if (dev < 64) configured[dev] = true;
+    if (dev < 64) configured[dev].store(true, std::memory_order_relaxed);
     return cudaSuccess;
 }
 
-template <int QT, int MODE, int CG>
+template <int QT, int MODE, int CG, int WIDE>
 static void fill_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute& attr, int grid, cudaStream_t stream) {
-    using Cfg = GemmCfg<QT, MODE, CG>;
+    using Cfg = GemmCfg<QT, MODE, CG, WIDE>;
     cfg = cudaLaunchConfig_t{};
     cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
     cfg.blockDim = dim3(kGemmThreads, 1, 1);
@@ -40,55 +43,63 @@ static void fill_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute& attr, int 
     cfg.numAttrs = 1;
 }
 
-template <int QT, int MODE, int CG>
+template <int QT, int MODE, int CG, int WIDE>
 static int launch_one(const GemmArgs& args, int grid, cudaStream_t stream) {
-    cudaError_t e = configure<QT, MODE, CG>();
+    cudaError_t e = configure<QT, MODE, CG, WIDE>();
     if (e != cudaSuccess) return static_cast<int>(e);
     if (CG == 1) {
-        mmq_gemm_kernel<QT, MODE, CG><<<grid, kGemmThreads, GemmCfg<QT, MODE, CG>::kSmemBytes, stream>>>(args);
+        mmq_gemm_kernel<QT, MODE, CG, WIDE><<<grid, kGemmThreads, GemmCfg<QT, MODE, CG, WIDE>::kSmemBytes, stream>>>(args);
         return static_cast<int>(cudaGetLastError());
     }
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr;
-    fill_config<QT, MODE, CG>(cfg, attr, grid, stream);
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, mmq_gemm_kernel<QT, MODE, CG>, args));
+    fill_config<QT, MODE, CG, WIDE>(cfg, attr, grid, stream);
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, mmq_gemm_kernel<QT, MODE, CG, WIDE>, args));
+}
+
+template <int QT, int MODE, int CG>
+static int launch_width(int wide, const GemmArgs& args, int grid, cudaStream_t stream) {
+    return wide ? launch_one<QT, MODE, CG, 1>(args, grid, stream) : launch_one<QT, MODE, CG, 0>(args, grid, stream);
 }
 
 // Most CTA pairs of this kernel that can be resident at once on the current device (0: pairs
 // cannot be launched here).
 template <int QT, int MODE>
 static int max_pairs_one() {
-    static int cached[64] = {};
+    static std::atomic<int> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    if (dev < 64 && cached[dev] != 0) return cached[dev] > 0 ? cached[dev] : 0;
+    if (dev < 64) {
+        const int c = cached[dev].load(std::memory_order_relaxed);
+        if (c != 0) return c > 0 ? c : 0;
+    }
     int n = 0;
-    if (configure<QT, MODE, 2>() == cudaSuccess) {
+    if (configure<QT, MODE, 2, 0>() == cudaSuccess) {   // both tile widths use the same threads and shared memory
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr;
         int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        fill_config<QT, MODE, 2>(cfg, attr, sms & ~1, nullptr);
-        if (cudaOccupancyMaxActiveClusters(&n, mmq_gemm_kernel<QT, MODE, 2>, &cfg) != cudaSuccess) {
+        fill_config<QT, MODE, 2, 0>(cfg, attr, sms & ~1, nullptr);
+        if (cudaOccupancyMaxActiveClusters(&n, mmq_gemm_kernel<QT, MODE, 2, 0>, &cfg) != cudaSuccess) {
             (void)cudaGetLastError();
             n = 0;
         }
     } else {
         (void)cudaGetLastError();
     }
-    if (dev < 64) cached[dev] = n > 0 ? n : -1;
+    if (dev < 64) cached[dev].store(n > 0 ? n : -1, std::memory_order_relaxed);
     return n;
 }
 
 #define TGO_CAT2(a, b) a##b
 #define TGO_CAT(a, b) TGO_CAT2(a, b)
 
-int TGO_CAT(launch_gemm_, TGO_QT)(int mode, int cta_group, const GemmArgs& args, int grid, cudaStream_t stream) {
+int TGO_CAT(launch_gemm_, TGO_QT)(int mode, int cta_group, int wide, const GemmArgs& args, int grid, cudaStream_t stream) {
     if (cta_group == 2)
-        return mode == kFwd ? launch_one<TGO_QT, kFwd, 2>(args, grid, stream)
-                            : launch_one<TGO_QT, kBwd, 2>(args, grid, stream);
-    return mode == kFwd ? launch_one<TGO_QT, kFwd, 1>(args, grid, stream)
-                        : launch_one<TGO_QT, kBwd, 1>(args, grid, stream);
+        return mode == kFwd ? launch_width<TGO_QT, kFwd, 2>(wide, args, grid, stream)
+                            : launch_width<TGO_QT, kBwd, 2>(wide, args, grid, stream);
+    return mode == kFwd ? launch_width<TGO_QT, kFwd, 1>(wide, args, grid, stream)
+                        : launch_width<TGO_QT, kBwd, 1>(wide, args, grid, stream);
 }
 
 int TGO_CAT(max_pairs_, TGO_QT)(int mode) {

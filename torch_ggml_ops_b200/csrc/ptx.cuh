@@ -51,10 +51,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
@@ -77,7 +73,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 enum : int {
     kAbortRawEmpty = 1, kAbortRawFull = 2, kAbortActEmpty = 3, kAbortActFull = 4,
     kAbortWgtEmpty = 5, kAbortWgtFull = 6, kAbortAccEmpty = 7, kAbortAccFull = 8,
-    kAbortDrain = 9
+    kAbortDrain = 9, kAbortSelfTest = 10
 };
 
 // Wait limit in SM clock cycles (~1 s at the clocks seen under load).
@@ -86,7 +82,7 @@ constexpr long long kWaitLimitCycles = 2000000000LL;
 // Bounded wait on one phase of an mbarrier.  `abort_word` is a CTA-shared int: non-zero means
 // some role already gave up, and everyone else leaves as soon as it sees that.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word,
-                                          int code) {
+                                          int code, long long limit_cycles = kWaitLimitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t polls = 0;
@@ -97,7 +93,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 #endif
         if ((++polls & 63u) == 0) {
             if (*abort_word != 0) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit_cycles) {
                 atomicCAS(const_cast<int*>(abort_word), 0, code);
                 return false;
             }
@@ -135,14 +131,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(cluster_bar), "r"(x), "r"(y)
         : "memory");
 }
-// 1-D bulk copy global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
-                                          uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
-        : "memory");
-}
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
@@ -174,20 +162,9 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
                  : "memory");
 }
 
-// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate.  One thread issues.
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// The same with both shared-memory descriptors given as (low word, common high word): within one
-// kernel only the start-address field (low word) differs from UMMA to UMMA.
+// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate.  One thread issues.  Both
+// shared-memory descriptors are given as (low word, common high word): within one kernel only the
+// start-address field (low word) differs from UMMA to UMMA.
 __device__ __forceinline__ void umma_bf16_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
                                                uint32_t desc_hi, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -218,18 +195,6 @@ __device__ __forceinline__ void umma_bf16_lohi_pair(uint32_t d_tmem, uint32_t a_
         ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
-// D[tmem] (+)= A[smem] * B[smem], int8 inputs, int32 accumulate.
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                        uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
-        "}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 // The mbarrier gets one arrival once every UMMA issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
@@ -254,48 +219,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
-// 32 lanes x 32 consecutive 32-bit columns.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // ------------------------------------------------------------------ UMMA descriptors
-// Shared-memory matrix descriptor, 128-byte swizzle, for a tile whose base is 1024-byte aligned.
-//   K-major operand  [rows][64 bf16]: 8-row groups 1024 B apart (SBO); LBO unused.
-//   MN-major operand [red rows][64 bf16 along MN]: 8 reduction rows per 1024 B (SBO), the next
-//   64 MN elements `lbo_bytes` further on (LBO).
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= 1ull << 46;  // descriptor version for this architecture
-    d |= 2ull << 61;  // SWIZZLE_128B
-    return d;
-}
+// The shared-memory matrix descriptors (128-byte swizzle, tile base 1024-byte aligned) are built
+// in the kernel: K-major operand [rows][64 bf16] with 8-row groups 1024 B apart (SBO), MN-major
+// operand [red rows][64 bf16 along MN] with 8 reduction rows per 1024 B (SBO) and the next 64 MN
+// elements LBO bytes further on.
 // Instruction descriptor: bf16 x bf16 -> fp32, M = 128, N = n (multiple of 16, 16..256).
 __device__ __forceinline__ uint32_t umma_idesc_bf16(uint32_t n, uint32_t a_mn_major,
                                                     uint32_t b_mn_major, uint32_t m = 128u) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (a_mn_major << 15) | (b_mn_major << 16) |
            ((n >> 3) << 17) | ((m >> 4) << 24);
 }
-// int8 x int8 -> int32 (signed both), M = 128.
-__device__ __forceinline__ uint32_t umma_idesc_s8(uint32_t n) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-}
-
 }  // namespace tgo

@@ -140,17 +140,18 @@ __global__ void __launch_bounds__(kRouteBlock) route_scatter_kernel(const int32_
     }
 }
 
-// dst[r][:] = src[index[r] / divisor][:], rows of `width` bf16 (width * 2 a multiple of 16).
-__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ index,
-                                                          int divisor, uint4* __restrict__ dst, long long n_rows,
-                                                          int vec_per_row) {
+// dst[r][:] = src[index[r] / divisor][:], rows of `width` bf16 (width * 2 a multiple of 16); an
+// index that is negative or names a row at or beyond src_rows gives a row of zeros.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ src, long long src_rows,
+                                                          const int32_t* __restrict__ index, int divisor,
+                                                          uint4* __restrict__ dst, long long n_rows, int vec_per_row) {
     const long long total = n_rows * vec_per_row;
     for (long long v = blockIdx.x * 256LL + threadIdx.x; v < total; v += 256LL * gridDim.x) {
         const long long r = v / vec_per_row;
         const int c = static_cast<int>(v - r * vec_per_row);
         const int s = index[r];
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (s >= 0) val = src[static_cast<long long>(s / divisor) * vec_per_row + c];
+        if (s >= 0 && s / divisor < src_rows) val = src[static_cast<long long>(s / divisor) * vec_per_row + c];
         dst[v] = val;
     }
 }
@@ -281,15 +282,16 @@ int tgo_route_sort(const int32_t* expert_ids, int64_t n_pairs, int64_t num_exper
     return launch_check("routing kernel launch failed");
 }
 
-int tgo_gather_rows(const void* src, const int32_t* index, int64_t divisor, void* dst, int64_t n_rows, int64_t width,
-                    void* stream) {
+int tgo_gather_rows(const void* src, int64_t src_rows, const int32_t* index, int64_t divisor, void* dst, int64_t n_rows,
+                    int64_t width, void* stream) {
     if (src == nullptr || index == nullptr || dst == nullptr) return route_fail(TGO_E_ARG, "null pointer");
+    if (src_rows <= 0) return route_fail(TGO_E_ARG, "gather needs at least one source row");
     if (n_rows <= 0 || width <= 0 || (width * 2) % 16 != 0 || divisor <= 0 || divisor > INT32_MAX)
         return route_fail(TGO_E_ARG, "gather needs rows > 0, a row length that is a multiple of 8 and divisor > 0");
     if (!aligned16(src) || !aligned16(dst)) return route_fail(TGO_E_ARG, "data pointers must be 16-byte aligned");
     const int vec = static_cast<int>(width / 8);
     gather_rows_kernel<<<grid_for(n_rows * vec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(src), index, static_cast<int>(divisor), static_cast<uint4*>(dst), n_rows, vec);
+        static_cast<const uint4*>(src), src_rows, index, static_cast<int>(divisor), static_cast<uint4*>(dst), n_rows, vec);
     return launch_check("gather_rows_kernel launch failed");
 }
 

@@ -6,6 +6,7 @@
 // host synchronisation and no device-to-host read on any path except tgo_device_status.
 #include "../../include/tgo_mmq.h"
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -42,20 +43,23 @@ static int fail(int code, const char* fmt, ...) {
 static int cuda_fail(cudaError_t e, const char* what) {
     return fail(TGO_E_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
 }
+static int check_status_if_asked(cudaStream_t stream);
 
 // Error setter for the other translation units of the library.
 int route_fail(int code, const char* msg) { return fail(code, "%s", msg); }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Per-device caches below are relaxed atomics: two host threads that make their first call on a
+// device at the same time both compute the same value and store it.
 static int num_sms() {
-    static int cached[64] = {};
+    static std::atomic<int> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (dev < 64 && cached[dev] > 0) return cached[dev];
+    if (dev < 64 && cached[dev].load(std::memory_order_relaxed) > 0) return cached[dev].load(std::memory_order_relaxed);
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    if (dev < 64) cached[dev] = n;
+    if (dev < 64) cached[dev].store(n, std::memory_order_relaxed);
     return n;
 }
 
@@ -216,12 +220,13 @@ static int copy_bytes_of(int qt) {
 
 // ------------------------------------------------------------------ tile-list builder
 // Workspace layout: int32 count at byte 0, int4 tasks from byte 16.
-// One CTA: per group, the number of token tiles ceil(rows / 256); exclusive prefix sum; each
-// group then writes its tiles, split evenly and rounded up to 16 tokens.
+// One CTA: per group, the number of token tiles ceil(rows / max_tok); exclusive prefix sum; each
+// group then writes its tiles, split evenly and rounded up to 16 tokens.  max_tok is 256 (one
+// accumulator per tile) or 512 (wide tiles: both accumulators share every decoded weight step).
 __global__ void __launch_bounds__(256) build_tiles_kernel(const int64_t* __restrict__ experts,
                                                           const int32_t* __restrict__ offsets, int num_groups,
                                                           int num_experts, int rows, int4* __restrict__ tasks,
-                                                          int* __restrict__ count, int capacity) {
+                                                          int* __restrict__ count, int capacity, int max_tok) {
     __shared__ int warp_sums[8];
     __shared__ int chunk_total;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -235,7 +240,7 @@ __global__ void __launch_bounds__(256) build_tiles_kernel(const int64_t* __restr
             end = offsets[g];
             beg = g > 0 ? offsets[g - 1] : 0;
             const bool valid = e >= 0 && e < num_experts && beg >= 0 && beg < end && end <= rows;
-            if (valid) nt = (end - beg + kTileTok - 1) / kTileTok;
+            if (valid) nt = (end - beg + max_tok - 1) / max_tok;
         }
         int incl = nt;
 #pragma unroll
@@ -314,15 +319,36 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
     for (int c = 0; c < 4; ++c) dst[c] = o[c];
 }
 
+// ------------------------------------------------------------------ wait self-test
+// One warp waits on an mbarrier that nobody ever arrives on, with a short limit: the wait gives up,
+// sets the abort word, and the kernel records the code in the status word exactly as the GEMM
+// kernel's exit path does.  No copy, no UMMA and no TMEM allocation is in flight.
+__global__ void __launch_bounds__(64) wait_selftest_kernel(long long limit_cycles, int* status) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_word;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_word = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0)   // one lane per warp; the second warp leaves through the abort word or its own limit
+        ok = mbar_wait(smem_u32(&bar), 0u, &abort_word, kAbortSelfTest, limit_cycles);
+    __syncthreads();
+    if (threadIdx.x == 0 && (!ok || abort_word != 0) && status != nullptr)
+        atomicCAS(status, 0, abort_word | (static_cast<int>(blockIdx.x) << 8));
+}
+
 // ------------------------------------------------------------------ GEMM dispatch
-static int dispatch_gemm(int qt, int mode, int cta_group, const GemmArgs& args, int grid, cudaStream_t stream) {
+static int dispatch_gemm(int qt, int mode, int cta_group, int wide, const GemmArgs& args, int grid, cudaStream_t stream) {
     int e;
     switch (qt) {
-        case QT_Q3_K: e = launch_gemm_11(mode, cta_group, args, grid, stream); break;
-        case QT_Q4_K: e = launch_gemm_12(mode, cta_group, args, grid, stream); break;
-        case QT_Q5_K: e = launch_gemm_13(mode, cta_group, args, grid, stream); break;
-        case QT_Q6_K: e = launch_gemm_14(mode, cta_group, args, grid, stream); break;
-        case QT_IQ2_S: e = launch_gemm_22(mode, cta_group, args, grid, stream); break;
+        case QT_Q3_K: e = launch_gemm_11(mode, cta_group, wide, args, grid, stream); break;
+        case QT_Q4_K: e = launch_gemm_12(mode, cta_group, wide, args, grid, stream); break;
+        case QT_Q5_K: e = launch_gemm_13(mode, cta_group, wide, args, grid, stream); break;
+        case QT_Q6_K: e = launch_gemm_14(mode, cta_group, wide, args, grid, stream); break;
+        case QT_IQ2_S: e = launch_gemm_22(mode, cta_group, wide, args, grid, stream); break;
         default: return fail(TGO_E_ARG, "unsupported quant_type: %d", qt);
     }
     if (e != 0) return cuda_fail(static_cast<cudaError_t>(e), "mmq_gemm_kernel launch");
@@ -348,6 +374,35 @@ static int wanted_cta_group() {
         return (e != nullptr && e[0] == '0') ? 1 : 2;
     }();
     return v;
+}
+
+// TGO_WIDE_TILES=0 / 1 forces tiles of at most 256 / 512 tokens (read at every call so that a test
+// can switch it); unset: chosen per call from the problem size.
+static int wide_tiles_env() {
+    const char* e = getenv("TGO_WIDE_TILES");
+    if (e == nullptr || e[0] == '\0') return -1;
+    return e[0] == '0' ? 0 : 1;
+}
+
+static int build_tiles(const int64_t* expert_indices, const int32_t* expert_offsets, int64_t num_groups,
+                       int64_t num_experts, int64_t rows, void* workspace, int64_t workspace_bytes, int max_tok,
+                       cudaStream_t stream);
+
+// Debug aid (environment TGO_CHECK_STATUS=1): wait for the stream after every matmul launch and
+// turn a recorded wait time-out into an error of that call.  Off by default: the operators never
+// synchronise; a production caller polls tgo_device_status at a point where it synchronises anyway.
+static int check_status_if_asked(cudaStream_t stream) {
+    const char* e = getenv("TGO_CHECK_STATUS");
+    if (e == nullptr || e[0] == '\0' || e[0] == '0') return TGO_OK;
+    const cudaError_t ce = cudaStreamSynchronize(stream);
+    if (ce != cudaSuccess) return cuda_fail(ce, "cudaStreamSynchronize");
+    int v = 0;
+    const int rc = tgo_device_status(&v);
+    if (rc != TGO_OK) return rc;
+    if (v != 0)
+        return fail(TGO_E_DEVICE, "a kernel gave up a bounded wait: code %d in block %d (outputs of that launch are incomplete)",
+                    v & 0xFF, v >> 8);
+    return TGO_OK;
 }
 
 struct Problem {
@@ -410,7 +465,6 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
             rc = make_act_maps(a.act_maps[s], p.act[src], p.rows, red);
             if (rc != TGO_OK) return rc;
         }
-        a.wgt[s] = static_cast<const uint8_t*>(p.wgt[s < p.nsets ? s : 0]);
         a.out[s] = static_cast<__nv_bfloat16*>(p.out[(p.mode == kFwd && s < p.nsets) ? s : 0]);
     }
     const int64_t bb = tgo_block_bytes(p.qt);
@@ -421,8 +475,6 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
         if (rc != TGO_OK) return rc;
     }
     a.wgt_row_bytes = static_cast<int>((p.K / 256) * bb);
-    a.expert_bytes = p.N * (p.K / 256) * bb;
-    a.wgt_bytes = a.expert_bytes * p.E;
     a.status = status_ptr();
     a.iq2s_grid = grid_ptr();
     if (a.status == nullptr || a.iq2s_grid == nullptr) return fail(TGO_E_CUDA, "cudaGetSymbolAddress failed");
@@ -430,7 +482,6 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
     a.out_features = static_cast<int>(p.N);
     a.in_features = static_cast<int>(p.K);
     a.nsets = p.nsets;
-    a.num_experts = static_cast<int>(p.E);
 
     int cg = wanted_cta_group();
     int pairs = 0;
@@ -440,27 +491,64 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
     }
     const int64_t tile_m = static_cast<int64_t>(kTileM) * cg;
     const int64_t mtiles = p.mode == kFwd ? ((p.N + tile_m - 1) / tile_m) * p.nsets : p.K / tile_m;
+    const int64_t limit = cg == 2 ? pairs : num_sms();
+    // Tiles of up to 512 tokens (two accumulators sharing each decoded weight step) halve the
+    // decode work per output element.  They pay when the 256-token tiles would not all run at
+    // once and the token tiles are mostly full: always for dense inputs of that size, for grouped
+    // inputs when the mean group has at least 384 rows (measured: with a mean of 256 rows per
+    // group most wide tiles would be half empty and the coarser tiles balance worse).  Host-visible
+    // sizes only: the groups' real sizes are known on the device alone.
+    const int wide_env = wide_tiles_env();
+    bool wide = ((p.rows + kTileTok - 1) / kTileTok) * mtiles > limit;
+    if (p.experts != nullptr && p.rows < 384 * p.groups) wide = false;
+    if (wide_env >= 0) wide = wide_env != 0;
+    const int max_tok = wide ? kWideTok : kTileTok;
     int64_t max_tasks;
     if (p.experts == nullptr) {
-        a.dense_tasks = static_cast<int>((p.rows + kTileTok - 1) / kTileTok);
+        a.dense_tasks = static_cast<int>((p.rows + max_tok - 1) / max_tok);
         a.dense_tok = static_cast<int>((((p.rows + a.dense_tasks - 1) / a.dense_tasks) + 15) & ~15LL);
         max_tasks = a.dense_tasks;
     } else {
         const int64_t cap = task_capacity(p.rows, p.groups);
-        rc = tgo_build_tiles(p.experts, p.offsets, p.groups, p.E, p.rows, p.ws, p.ws_bytes, stream);
+        rc = build_tiles(p.experts, p.offsets, p.groups, p.E, p.rows, p.ws, p.ws_bytes, max_tok, stream);
         if (rc != TGO_OK) return rc;
         a.task_count = static_cast<const int*>(p.ws);
         a.tasks = reinterpret_cast<const int4*>(static_cast<const uint8_t*>(p.ws) + 16);
         max_tasks = cap;
     }
     int64_t grid = max_tasks * mtiles;  // persistent CTAs (pairs) never outnumber the tiles
-    const int64_t limit = cg == 2 ? pairs : num_sms();
     if (grid > limit) grid = limit;
     if (grid < 1) grid = 1;
     if (getenv("TGO_DEBUG_LAUNCH") != nullptr)
         fprintf(stderr, "tgo launch: mode %d cta_group %d pairs %d grid %lld tiles<=%lld\n", p.mode, cg, pairs,
                 (long long)(grid * cg), (long long)(max_tasks * mtiles));
-    return dispatch_gemm(p.qt, p.mode, cg, a, static_cast<int>(grid * cg), stream);
+    rc = dispatch_gemm(p.qt, p.mode, cg, wide ? 1 : 0, a, static_cast<int>(grid * cg), stream);
+    if (rc != TGO_OK) return rc;
+    return check_status_if_asked(stream);
+}
+
+static int build_tiles(const int64_t* expert_indices, const int32_t* expert_offsets, int64_t num_groups,
+                       int64_t num_experts, int64_t rows, void* workspace, int64_t workspace_bytes, int max_tok,
+                       cudaStream_t stream) {
+    if (expert_indices == nullptr || expert_offsets == nullptr || workspace == nullptr)
+        return fail(TGO_E_ARG, "null pointer");
+    if (num_groups <= 0) return fail(TGO_E_ARG, "grouped MMQ requires at least one active expert");
+    if (num_experts <= 0) return fail(TGO_E_ARG, "packed_weight must contain at least one expert");
+    if (rows <= 0) return fail(TGO_E_ARG, "zero-row inputs are not supported");
+    if (rows > INT32_MAX || num_groups > INT32_MAX || num_experts > INT32_MAX)
+        return fail(TGO_E_ARG, "a dimension exceeds the kernel limit of 2^31-1");
+    const int64_t need = tgo_grouped_workspace_bytes(rows, num_groups);
+    if (workspace_bytes < need)
+        return fail(TGO_E_WORKSPACE, "workspace has %lld bytes, need %lld", (long long)workspace_bytes, (long long)need);
+    if (!aligned16(workspace)) return fail(TGO_E_ARG, "workspace pointer must be 16-byte aligned");
+    int* count = static_cast<int*>(workspace);
+    int4* tasks = reinterpret_cast<int4*>(static_cast<uint8_t*>(workspace) + 16);
+    build_tiles_kernel<<<1, 256, 0, stream>>>(expert_indices, expert_offsets, static_cast<int>(num_groups),
+                                              static_cast<int>(num_experts), static_cast<int>(rows), tasks, count,
+                                              static_cast<int>(task_capacity(rows, num_groups)), max_tok);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "build_tiles_kernel launch");
+    return TGO_OK;
 }
 
 // ------------------------------------------------------------------ built-in tile-list scratch
@@ -474,19 +562,20 @@ static __device__ __align__(256) unsigned char g_static_tile_scratch[kStaticScra
 // handle for the runtime, never an address a kernel may be given, so the address is looked up
 // once per device (with that device current) and remembered.
 static int static_scratch_ptr(void** out) {
-    static void* cached[64] = {};
+    static std::atomic<void*> cached[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev < 0 || dev >= 64) return fail(TGO_E_ARG, "device index %d is outside the supported range 0..63", dev);
-    if (cached[dev] == nullptr) {
-        void* p = nullptr;
+    void* p = cached[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        // two threads racing here both get the same address from the runtime and store it
         e = cudaGetSymbolAddress(&p, g_static_tile_scratch);
         if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(built-in tile scratch)");
         if (p == nullptr) return fail(TGO_E_CUDA, "cudaGetSymbolAddress returned a null address for the built-in tile scratch");
-        cached[dev] = p;
+        cached[dev].store(p, std::memory_order_release);
     }
-    *out = cached[dev];
+    *out = p;
     return TGO_OK;
 }
 
@@ -514,6 +603,17 @@ int tgo_device_status(int* status) {
         if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyToSymbol");
     }
     *status = v;
+    return TGO_OK;
+}
+
+int tgo_selftest_wait_timeout(int64_t limit_cycles, void* stream) {
+    if (limit_cycles < 1000 || limit_cycles > 200000000LL)
+        return fail(TGO_E_ARG, "limit_cycles must be in 1000..200000000 (at most about a tenth of a second)");
+    int* status = status_ptr();
+    if (status == nullptr) return fail(TGO_E_CUDA, "cudaGetSymbolAddress failed");
+    wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(limit_cycles, status);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "wait_selftest_kernel launch");
     return TGO_OK;
 }
 
@@ -564,26 +664,12 @@ int64_t tgo_grouped_workspace_bytes(int64_t rows, int64_t num_groups) {
 }
 
 int tgo_build_tiles(const int64_t* expert_indices, const int32_t* expert_offsets, int64_t num_groups,
-                    int64_t num_experts, int64_t rows, void* workspace, int64_t workspace_bytes, void* stream) {
-    if (expert_indices == nullptr || expert_offsets == nullptr || workspace == nullptr)
-        return fail(TGO_E_ARG, "null pointer");
-    if (num_groups <= 0) return fail(TGO_E_ARG, "grouped MMQ requires at least one active expert");
-    if (num_experts <= 0) return fail(TGO_E_ARG, "packed_weight must contain at least one expert");
-    if (rows <= 0) return fail(TGO_E_ARG, "zero-row inputs are not supported");
-    if (rows > INT32_MAX || num_groups > INT32_MAX || num_experts > INT32_MAX)
-        return fail(TGO_E_ARG, "a dimension exceeds the kernel limit of 2^31-1");
-    const int64_t need = tgo_grouped_workspace_bytes(rows, num_groups);
-    if (workspace_bytes < need)
-        return fail(TGO_E_WORKSPACE, "workspace has %lld bytes, need %lld", (long long)workspace_bytes, (long long)need);
-    if (!aligned16(workspace)) return fail(TGO_E_ARG, "workspace pointer must be 16-byte aligned");
-    int* count = static_cast<int*>(workspace);
-    int4* tasks = reinterpret_cast<int4*>(static_cast<uint8_t*>(workspace) + 16);
-    build_tiles_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        expert_indices, expert_offsets, static_cast<int>(num_groups), static_cast<int>(num_experts),
-        static_cast<int>(rows), tasks, count, static_cast<int>(task_capacity(rows, num_groups)));
-    const cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, "build_tiles_kernel launch");
-    return TGO_OK;
+                    int64_t num_experts, int64_t rows, int64_t max_tile_tokens, void* workspace,
+                    int64_t workspace_bytes, void* stream) {
+    if (max_tile_tokens != kTileTok && max_tile_tokens != kWideTok)
+        return fail(TGO_E_ARG, "max_tile_tokens must be %d or %d; got %lld", kTileTok, kWideTok, (long long)max_tile_tokens);
+    return build_tiles(expert_indices, expert_offsets, num_groups, num_experts, rows, workspace, workspace_bytes,
+                       static_cast<int>(max_tile_tokens), static_cast<cudaStream_t>(stream));
 }
 
 int tgo_grouped_fwd(const void* x, const void* w0, const void* w1, void* y0, void* y1,

@@ -73,7 +73,9 @@ class ExpertParallel:
             from . import native
 
             flat = topk_ids.reshape(-1).to(torch.int32)
-            send_perm, pair_to_sorted, _, ends = native.route_sort(flat, self.num_experts)
+            # ids outside [0, E) are left out of the sort: their entries must not stay uninitialised
+            pre = {"s2p": torch.full((flat.numel(),), -1, dtype=torch.int32, device=device)}
+            send_perm, pair_to_sorted, _, ends = native.route_sort(flat, self.num_experts, out=pre)
             ends = ends.to(torch.int64)
             send_counts = (ends - torch.cat([ends.new_zeros(1), ends[:-1]])).reshape(W, EL)
         else:
@@ -91,6 +93,8 @@ class ExpertParallel:
         totals = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).cpu()
         send_splits = [int(v) for v in totals[0]]
         recv_splits = [int(v) for v in totals[1]]
+        if sum(send_splits) != flat.numel():
+            raise ValueError(f"topk_ids holds {flat.numel() - sum(send_splits)} expert ids outside [0, {self.num_experts})")
         rows_recv = sum(recv_splits)
         # received buffer order: (source rank, local expert, arrival); wanted: (local expert, source rank, arrival)
         cnt = recv_counts.reshape(-1)                          # index s * EL + e

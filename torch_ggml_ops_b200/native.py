@@ -21,16 +21,17 @@ SIGNATURES = {
     "tgo_last_error": (ctypes.c_char_p, []),
     "tgo_block_bytes": (_i64, [_i32]),
     "tgo_device_status": (_i32, [ctypes.POINTER(ctypes.c_int)]),
+    "tgo_selftest_wait_timeout": (_i32, [_i64, _vp]),
     "tgo_dequantize_bf16": (_i32, [_vp, _i64, _i32, _vp, _vp]),
     "tgo_mmq_fwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "tgo_mmq_dx": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "tgo_grouped_workspace_bytes": (_i64, [_i64, _i64]),
-    "tgo_build_tiles": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "tgo_build_tiles": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tgo_grouped_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
     "tgo_grouped_dx": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
     "tgo_route_workspace_bytes": (_i64, [_i64, _i64]),
     "tgo_route_sort": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
-    "tgo_gather_rows": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _vp]),
+    "tgo_gather_rows": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp]),
     "tgo_combine_rows": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tgo_quantize_q8": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     "tgo_ep_plan": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -38,7 +39,7 @@ SIGNATURES = {
     "tgo_ep_pull": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tgo_ep_token_maps": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp]),
     "tgo_ep_dispatch_tokens": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
-    "tgo_ep_expand": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
+    "tgo_ep_expand": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp]),
     "tgo_ep_reduce": (_i32, [_vp, _vp, _i64, _i64, _vp, _i64, _vp]),
     "tgo_ep_pull_tokens": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tgo_grouped_fwd_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
@@ -90,6 +91,12 @@ def device_status() -> int:
     return out.value
 
 
+def selftest_wait_timeout(limit_cycles: int = 1_000_000, stream=None) -> None:
+    """Launches the kernel whose bounded wait runs out on purpose (see ``tgo_selftest_wait_timeout``);
+    ``device_status()`` then reports code 10."""
+    check(lib().tgo_selftest_wait_timeout(limit_cycles, _stream(stream)), "tgo_selftest_wait_timeout")
+
+
 def dequantize_bf16(packed, quant_type: int, out=None, stream=None):
     import torch
 
@@ -118,9 +125,9 @@ def grouped_workspace_bytes(rows: int, groups: int) -> int:
     return int(lib().tgo_grouped_workspace_bytes(rows, groups))
 
 
-def build_tiles(expert_indices, expert_offsets, num_experts, rows, workspace, stream=None) -> None:
+def build_tiles(expert_indices, expert_offsets, num_experts, rows, workspace, stream=None, max_tile_tokens=256) -> None:
     check(lib().tgo_build_tiles(_ptr(expert_indices), _ptr(expert_offsets), expert_indices.numel(), num_experts, rows,
-                                _ptr(workspace), workspace.numel(), _stream(stream)), "tgo_build_tiles")
+                                max_tile_tokens, _ptr(workspace), workspace.numel(), _stream(stream)), "tgo_build_tiles")
 
 
 def grouped_fwd(x, w0, w1, y0, y1, expert_indices, expert_offsets, num_experts, rows, out_features, in_features,
@@ -174,7 +181,7 @@ def gather_rows(src, index, divisor=1, stream=None):
     import torch
 
     dst = torch.empty((index.numel(), src.shape[1]), dtype=src.dtype, device=src.device)
-    check(lib().tgo_gather_rows(_ptr(src), _ptr(index), divisor, _ptr(dst), index.numel(), src.shape[1],
+    check(lib().tgo_gather_rows(_ptr(src), src.shape[0], _ptr(index), divisor, _ptr(dst), index.numel(), src.shape[1],
                                 _stream(stream)), "tgo_gather_rows")
     return dst
 
@@ -254,8 +261,8 @@ def ep_dispatch_tokens(src, dst_rank, top_k, my_rank, tokens_per_rank, token_buf
 
 def ep_expand(token_buffer, row_slot, n_rows_device, rows, stream=None) -> None:
     """rows[r] = token_buffer[row_slot[r]] for r < n_rows_device[0] (a device int32 tensor)."""
-    check(lib().tgo_ep_expand(_ptr(token_buffer), _ptr(row_slot), _ptr(n_rows_device), _ptr(rows), rows.shape[0],
-                              rows.shape[1], _stream(stream)), "tgo_ep_expand")
+    check(lib().tgo_ep_expand(_ptr(token_buffer), token_buffer.shape[0], _ptr(row_slot), _ptr(n_rows_device),
+                              _ptr(rows), rows.shape[0], rows.shape[1], _stream(stream)), "tgo_ep_expand")
 
 
 def ep_reduce(rows, slot_rows, top_k, partial_sums, stream=None) -> None:

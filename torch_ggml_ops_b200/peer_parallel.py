@@ -82,9 +82,11 @@ class PeerExpertParallel:
                 self.buf[name] = t
                 self.peers[name] = [t.data_ptr()]
         if self.token_level:
-            # a slot nobody has written yet must not name a row; peers write into this buffer from
-            # their first plan on, so everybody finishes the fill before anybody goes on
+            # a slot nobody has written yet must not name a row, and a row nobody has announced must
+            # not name a slot outside the token buffer; peers write into these buffers from their
+            # first plan on, so everybody finishes the fills before anybody goes on
             self.buf["slot_rows"].fill_(-1)
+            self.buf["row_slot"].fill_(-1)
             if self.world > 1:
                 dist.barrier(group=group)
         self.ws = torch.empty(native.grouped_workspace_bytes(self.cap, self.EL), dtype=torch.uint8, device=dev)
@@ -120,7 +122,13 @@ class PeerExpertParallel:
                 "scratch": torch.empty(2 * self.E, dtype=i32, device=dev),
                 "overflow": torch.zeros(1, dtype=i32, device=dev),
             }
+        if self.token_level and (topk_ids.shape[1] != self.top_k or topk_ids.shape[0] > self.tpr):
+            # every rank must take the same kind of exchange: a rank that fell back to one row per
+            # pair on its own would leave the owners' row -> slot maps unwritten
+            raise ValueError(f"this exchange was set up for top_k = {self.top_k} and at most {self.tpr} tokens per rank; "
+                             f"got top_k = {topk_ids.shape[1]}, {topk_ids.shape[0]} tokens")
         b = self._plan_bufs
+        b["overflow"].zero_()   # the flag describes this plan only
         _, p2s, _, _ = native.route_sort(flat, self.E, out=b)
         if self.world > 1:
             counts_all = b["counts_all"]
@@ -131,13 +139,21 @@ class PeerExpertParallel:
         self.overflow = overflow  # device flag: a row did not fit in `capacity_rows` (read it when convenient)
         plan = {"top_k": topk_ids.shape[1], "tokens": topk_ids.shape[0], "dst_rank": dst_rank, "dst_row": dst_row,
                 "indices": li, "offsets": lo, "token_level": False}
-        if self.token_level and plan["top_k"] == self.top_k and plan["tokens"] <= self.tpr:
+        if self.token_level:
             # the peers' maps are rewritten here; the exchanges that read them come after a fence
             native.ep_token_maps(dst_rank, dst_row, plan["tokens"], self.top_k, self.rank, self.tpr,
                                  self.peers["row_slot"], self.peers["slot_rows"])
             plan["token_level"] = True
             plan["n_rows"] = lo[self.EL - 1:]   # device int32: rows that exist in this rank's buffers
         return plan
+
+    def check_overflow(self) -> None:
+        """Raises if the last plan dropped routed pairs because a receive buffer (``capacity_rows``)
+        was too small: those pairs got zero outputs and contributed no gradient.  Reads one device
+        integer, so it waits for the stream; call it where the host synchronises anyway."""
+        if self.overflow is not None and int(self.overflow.item()) != 0:
+            raise RuntimeError(f"expert-parallel receive buffer overflow: capacity_rows = {self.cap} is too small for "
+                               "this routing; dropped pairs were computed as zeros")
 
     # ------------------------------------------------------------------ forward
     def forward(self, plan, x_tokens: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
