@@ -493,14 +493,13 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
     const int64_t mtiles = p.mode == kFwd ? ((p.N + tile_m - 1) / tile_m) * p.nsets : p.K / tile_m;
     const int64_t limit = cg == 2 ? pairs : num_sms();
     // Tiles of up to 512 tokens (two accumulators sharing each decoded weight step) halve the
-    // decode work per output element.  They pay when the 256-token tiles would not all run at
-    // once and the token tiles are mostly full: always for dense inputs of that size, for grouped
-    // inputs when the mean group has at least 384 rows (measured: with a mean of 256 rows per
-    // group most wide tiles would be half empty and the coarser tiles balance worse).  Host-visible
-    // sizes only: the groups' real sizes are known on the device alone.
+    // decode work per output element and the number of tiles.  Measured on B200 (Q4_K): dense
+    // M = 4096 gains 11 % forward and 20 % backward once the 256-token tiles no longer all run at
+    // once; grouped inputs lose 3-10 % whatever the mean group size (256, 512 or 2048 rows), because
+    // ragged groups leave the wide tiles part empty and the coarser tiles balance worse.  So: dense
+    // inputs only.  TGO_WIDE_TILES overrides the choice (tests run every case both ways).
     const int wide_env = wide_tiles_env();
-    bool wide = ((p.rows + kTileTok - 1) / kTileTok) * mtiles > limit;
-    if (p.experts != nullptr && p.rows < 384 * p.groups) wide = false;
+    bool wide = p.experts == nullptr && ((p.rows + kTileTok - 1) / kTileTok) * mtiles > limit;
     if (wide_env >= 0) wide = wide_env != 0;
     const int max_tok = wide ? kWideTok : kTileTok;
     int64_t max_tasks;
