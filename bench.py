@@ -11,12 +11,18 @@ bench/grouped_mmq_benchmark_common.py:228-239), on the MoE expert-projection con
 
 One step = one forward pass plus one input-gradient pass over the routed rows.
 
-* N = 1: the grouped operators on one GPU.  ``value`` is timed with inputs resident in HBM
-  (C-ABI calls, CUDA events); ``e2e`` is the same step through the public torch operators with
-  pinned host buffers copied in and results copied out inside the timed region.
-* N > 1 (under torchrun): expert-parallel.  Each rank owns 256/N experts and 8192 tokens; routed
-  rows travel to the owning GPU and back with one all-to-all each way in each direction
-  (4 per step, NCCL).  Weak scaling: per-GPU tokens are fixed.
+* N = 1: the grouped operators on one GPU.  ``value`` is timed with the expert-sorted rows
+  resident in HBM (C-ABI calls, CUDA events per launch).
+* N > 1 (under torchrun): expert-parallel.  Each rank owns 256/N experts and 8192 tokens; a token's
+  row goes once to every GPU that owns one of its experts and results come back, moved by this
+  library's peer-memory kernels over NVLink (NCCL carries only the per-expert counts and the
+  one-element fences between phases).  Weak scaling: per-GPU tokens are fixed.
+* every N: ``e2e`` is the expert-parallel step (tokens + top-k ids in, per-pair forward rows and
+  per-token gradients out; routing sort, dispatch and combine inside) with pinned host buffers
+  copied in and results copied out inside the timed region; ``parity`` compares sampled tokens of
+  every rank with the CPU oracle after the timed region; ``config5`` times and checks the
+  expert-parallel MoE feed-forward configuration (IQ2_S gate/up + Q6_K down, 65536 tokens split
+  over the GPUs).
 * ``--impl reference``: the reference semantics on the host CPU (dequantise the GGUF blocks, fp32
   ``torch.matmul`` per group) on a bounded sample of the same workload.  The reference's own
   kernels are ROCm-only and cannot run here.
@@ -190,6 +196,107 @@ def cpu_reference_arm(wl, steps, warmup, sample_experts=32, seed=2024):
                       f"dequantise + fp32 matmul fwd + dX, {steps} timed passes"}
 
 
+# ------------------------------------------------------------------------------ helpers of the GPU arm
+def bind_to_gpu_numa_node(gpu_index: int):
+    """Best effort: run this process (and so place its pinned host buffers) on the CPUs of the NUMA
+    node the GPU hangs off.  Returns the node, or None when the topology cannot be read."""
+    try:
+        bus = subprocess.run(["nvidia-smi", f"--id={gpu_index}", "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=20).stdout.strip().lower()
+        if not bus:
+            return None
+        bus = bus[-12:] if len(bus) > 12 else bus          # 00000000:1b:00.0 -> 0000:1b:00.0
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+        return node
+    except Exception:
+        return None
+
+
+def routing_weights(tokens, top_k, seed):
+    """Seeded positive routing weights that sum to one per token (stand-in for the router's softmax)."""
+    g = torch.Generator().manual_seed(seed)
+    w = torch.rand(tokens, top_k, generator=g) + 0.25
+    return w / w.sum(1, keepdim=True)
+
+
+def oracle_expert(qt, experts, n, k, seed, e):
+    """fp32 [n, k] weight of expert e of the synthetic stack (CPU oracle: the checker only)."""
+    from oracle import ref
+
+    raw = synthetic_expert_weights(qt, experts, n, k, seed, e, e + 1)
+    return torch.from_numpy(ref.dequantize(raw, qt).reshape(n, k))
+
+
+def rel_err(got, want):
+    return float(torch.linalg.vector_norm(got.double() - want.double()) / torch.linalg.vector_norm(want.double()))
+
+
+def projection_parity(wl, seed, ids_cpu, x_tok, dy_rows, y_rows, dx_tok, n_check):
+    """Forward rows and token gradients of `n_check` sampled tokens of this rank against the fp32
+    oracle (dequantise + matmul) on the experts those tokens hit."""
+    qt, E, N, K, top_k = wl["qt"], wl["experts"], wl["N"], wl["K"], wl["top_k"]
+    T = ids_cpu.shape[0]
+    pick = np.random.Generator(np.random.PCG64(99)).choice(T, size=min(n_check, T), replace=False)
+    cache = {}
+    got_y, want_y, got_dx, want_dx = [], [], [], []
+    for t in pick:
+        xt = x_tok[t].float().cpu()
+        acc = torch.zeros(K)
+        for s in range(top_k):
+            e = int(ids_cpu[t, s])
+            if e not in cache:
+                cache[e] = oracle_expert(qt, E, N, K, seed, e)
+            W = cache[e]
+            want_y.append(W @ xt)
+            got_y.append(y_rows[t * top_k + s].float().cpu())
+            acc += dy_rows[t * top_k + s].float().cpu() @ W
+        want_dx.append(acc)
+        got_dx.append(dx_tok[t].float().cpu())
+    return {"fwd_rel_err": rel_err(torch.stack(got_y), torch.stack(want_y)),
+            "dx_rel_err": rel_err(torch.stack(got_dx), torch.stack(want_dx)), "tokens_checked": int(len(pick)),
+            "experts_dequantised": len(cache)}
+
+
+def mlp_parity(c5, seed, ids_cpu, gate_w, x_tok, dy_tok, y_tok, dx_tok, n_check):
+    """The MoE feed-forward step of `n_check` sampled tokens against the fp32 oracle chain."""
+    E, H, F, top_k = c5["experts"], c5["hidden"], c5["ffn"], c5["top_k"]
+    T = ids_cpu.shape[0]
+    pick = np.random.Generator(np.random.PCG64(77)).choice(T, size=min(n_check, T), replace=False)
+    silu = lambda v: v * torch.sigmoid(v)  # noqa: E731
+    cache = {}
+    want_y, want_dx = [], []
+    for t in pick:
+        xt, dyt = x_tok[t].float().cpu(), dy_tok[t].float().cpu()
+        y, dx = torch.zeros(H), torch.zeros(H)
+        for s in range(top_k):
+            e = int(ids_cpu[t, s])
+            if e not in cache:
+                cache[e] = (oracle_expert(c5["qt_gate_up"], E, F, H, seed + 1, e), oracle_expert(c5["qt_gate_up"], E, F, H, seed + 2, e),
+                            oracle_expert(c5["qt_down"], E, H, F, seed + 3, e))
+            Wg, Wu, Wd = cache[e]
+            w = float(gate_w[t, s])
+            g, u = Wg @ xt, Wu @ xt
+            y += w * (Wd @ (silu(g) * u))
+            dh = w * (dyt @ Wd)
+            sg = torch.sigmoid(g)
+            dx += (dh * u * (sg * (1 + g * (1 - sg)))) @ Wg + (dh * silu(g)) @ Wu
+        want_y.append(y)
+        want_dx.append(dx)
+    idx = torch.from_numpy(pick.astype(np.int64))
+    return {"fwd_rel_err": rel_err(y_tok.float().cpu()[idx], torch.stack(want_y)),
+            "dx_rel_err": rel_err(dx_tok.float().cpu()[idx], torch.stack(want_dx)), "tokens_checked": int(len(pick)),
+            "experts_dequantised": len(cache)}
+
+
 # ------------------------------------------------------------------------------ GPU arm
 def gpu_arm(args):
     import torch.distributed as dist
@@ -197,6 +304,8 @@ def gpu_arm(args):
     import torch_ggml_ops_b200 as tgo
     from torch_ggml_ops_b200 import native
     from torch_ggml_ops_b200.expert_parallel import ExpertParallel
+    from torch_ggml_ops_b200.moe_parallel import PeerMoEMLP
+    from torch_ggml_ops_b200.peer_parallel import PeerExpertParallel
 
     wl = WORKLOAD
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -204,16 +313,18 @@ def gpu_arm(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    numa = bind_to_gpu_numa_node(local_rank)
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     qt, E, N, K, T, top_k = wl["qt"], wl["experts"], wl["N"], wl["K"], wl["tokens"], wl["top_k"]
     seed = 2024
-    ep = ExpertParallel(E)
-    EL = ep.experts_per_rank
+    EL = E // world
     w = torch.from_numpy(synthetic_expert_weights(qt, E, N, K, seed, rank * EL, (rank + 1) * EL)).to(dev)
-    ids = torch.from_numpy(synthetic_routing(T, E, top_k, wl["sigma"], seed + rank)).to(dev)
+    ids_cpu = synthetic_routing(T, E, top_k, wl["sigma"], seed + rank)
+    ids = torch.from_numpy(ids_cpu).to(dev)
+    ids32 = ids.to(torch.int32)
     g = torch.Generator(device=dev).manual_seed(seed + rank)
     x_tok = torch.randn(T, K, generator=g, device=dev).to(torch.bfloat16)
     dy_rows = torch.randn(T * top_k, N, generator=g, device=dev).to(torch.bfloat16)  # per routed row, token-major
@@ -225,20 +336,51 @@ def gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(ms):
+    def max_over_ranks(v):
         if world == 1:
-            return ms
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def timed_steps(fn, steps):
+        """`steps` calls of fn between barriers, CUDA events on the current stream, max over ranks (ms per call)."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / steps)
+
+    # ---------------------------------------------------------------- the expert-parallel step (every N)
+    # tokens + top-k expert ids in, per-pair forward rows and per-token input gradients out: device
+    # routing sort, dispatch to the owning GPU, grouped matmuls, return.  Receive buffers hold twice
+    # the mean load when experts are spread over several GPUs (the routing is skewed).
+    cap = R if world == 1 else 2 * R
+    pep = PeerExpertParallel(w, qt, E, N, K, capacity_rows=cap, tokens_per_rank=T if args.token_level else None, top_k=top_k)
+    y_out = [torch.empty(R, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    dx_out = [torch.empty(T, K, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+
+    def step_ep(x=x_tok, dy=dy_rows, b=0):
+        plan = pep.plan(ids32)
+        pep.forward(plan, x, out=y_out[b])
+        pep.grad_input(plan, dy, out=dx_out[b])
+        return y_out[b], dx_out[b]
+
     result = {}
+    if not args.profile:
+        for _ in range(max(args.warmup, 3)):
+            step_ep()
+    barrier()
     if world == 1:
         # ---------------------------------------------------------------- kernel-resident timing
-        plan = ep.plan(ids)
-        x_rows = ep.dispatch_tokens(plan, x_tok)              # [R, K] expert-major (local gather only)
-        dy_sorted = ep.dispatch_rows(plan, dy_rows)
-        ei, eo = plan.expert_indices, plan.expert_offsets
+        ep = ExpertParallel(E)
+        plan1 = ep.plan(ids)
+        x_rows = ep.dispatch_tokens(plan1, x_tok)              # [R, K] expert-major (local gather only)
+        dy_sorted = ep.dispatch_rows(plan1, dy_rows)
+        ei, eo = plan1.expert_indices, plan1.expert_offsets
         y = torch.empty(R, N, dtype=torch.bfloat16, device=dev)
         dx = torch.empty(R, K, dtype=torch.bfloat16, device=dev)
         ws = torch.empty(native.grouped_workspace_bytes(R, EL), dtype=torch.uint8, device=dev)
@@ -260,78 +402,21 @@ def gpu_arm(args):
         sampler = ClockSampler(local_rank)
         sampler.start()
         keep_busy_for(1.0, step_resident)
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps + 1)]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
         barrier()
         ev[0].record()
         for i in range(args.steps):
             native.grouped_fwd(x_rows, w, None, y, None, ei, eo, EL, R, N, K, qt, ws)
-            ev[3 * i + 1].record()
+            ev[2 * i + 1].record()
             native.grouped_dx(dy_sorted, None, w, None, dx, ei, eo, EL, R, N, K, qt, ws)
-            ev[3 * i + 2].record()
-            ev[3 * i + 3].record()
+            ev[2 * i + 2].record()
         barrier()
         clocks = sampler.stop()
-        total_ms = ev[0].elapsed_time(ev[3 * args.steps])
-        fwd_ms = float(np.mean([ev[3 * i].elapsed_time(ev[3 * i + 1]) for i in range(args.steps)]))
-        bwd_ms = float(np.mean([ev[3 * i + 1].elapsed_time(ev[3 * i + 2]) for i in range(args.steps)]))
-        status = native.device_status()
-        ms_step = max_over_ranks(total_ms / args.steps)
-
-        # ---------------------------------------------------------------- end to end through the public operators
-        xh = x_rows.cpu().pin_memory()
-        dyh = dy_sorted.cpu().pin_memory()
-        yh = torch.empty(R, N, dtype=torch.bfloat16).pin_memory()
-        dxh = torch.empty(R, K, dtype=torch.bfloat16).pin_memory()
-        # Three streams, two sets of device buffers: the host->device copy of step i+1 and the
-        # device->host copy of step i-1 overlap the matmuls of step i (PCIe is full duplex).  Every
-        # step still copies all of its inputs in and all of its results out inside the timed region.
-        s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-        xd = [torch.empty(R, K, dtype=torch.bfloat16, device=dev, requires_grad=True) for _ in range(2)]
-        dyd = [torch.empty(R, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]
-        ev_in = [torch.cuda.Event() for _ in range(2)]
-        ev_cmp = [torch.cuda.Event() for _ in range(2)]
-        ev_out = [torch.cuda.Event() for _ in range(2)]
-
-        def step_e2e(i):
-            b = i & 1
-            with torch.cuda.stream(s_in), torch.no_grad():
-                s_in.wait_event(ev_cmp[b])          # the matmuls that last read these buffers are done
-                xd[b].copy_(xh, non_blocking=True)
-                dyd[b].copy_(dyh, non_blocking=True)
-                ev_in[b].record(s_in)
-            with torch.cuda.stream(s_cmp):
-                s_cmp.wait_event(ev_in[b])
-                xd[b].grad = None
-                out = tgo.grouped_mmq(xd[b], w, ei, eo, qt, N)
-                out.backward(dyd[b])
-                ev_cmp[b].record(s_cmp)
-                grad = xd[b].grad
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_cmp[b])
-                out.record_stream(s_out)
-                grad.record_stream(s_out)
-                yh.copy_(out.detach(), non_blocking=True)
-                dxh.copy_(grad, non_blocking=True)
-                ev_out[b].record(s_out)
-
-        def run_e2e(n):
-            for st in (s_in, s_cmp, s_out):
-                st.wait_stream(torch.cuda.current_stream())
-            for i in range(n):
-                step_e2e(i)
-            for st in (s_in, s_cmp, s_out):
-                torch.cuda.current_stream().wait_stream(st)
-
-        run_e2e(3)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        run_e2e(args.steps)
-        e1.record()
-        barrier()
-        e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
-        h2d = xh.numel() * 2 + dyh.numel() * 2
-        d2h = yh.numel() * 2 + dxh.numel() * 2
+        total_ms = ev[0].elapsed_time(ev[2 * args.steps])
+        fwd_ms = float(np.mean([ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps)]))
+        bwd_ms = float(np.mean([ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps)]))
+        ms_step = total_ms / args.steps
+        result["ep_step_ms"] = timed_steps(step_ep, args.steps)   # the same work through routing + dispatch + combine
         launches = 4  # tile builder + GEMM, forward and backward
         peaks = json.load(open(ROOT / "MEASURED_PEAKS.json")) if (ROOT / "MEASURED_PEAKS.json").exists() else None
         # The launches are timed back to back inside a power-capped loop (a second of the same load
@@ -349,124 +434,90 @@ def gpu_arm(args):
             "hbm_gbs": bytes_dir / (ms * 1e-3) / 1e9, "hbm_frac": bytes_dir / (ms * 1e-3) / 1e9 / peak_hbm,
             "ms_per_launch": ms}
         result["roofline"] = dict(roof(fwd_ms), kernel="mmq_gemm_kernel<Q4_K, forward> (+ tile builder)",
-                                  traffic=MEASURED_DRAM_TRAFFIC.get("fwd"))
+                                  traffic=MEASURED_DRAM_TRAFFIC.get("fwd"), traffic_source=MEASURED_DRAM_TRAFFIC["source"])
         result["roofline_dx"] = dict(roof(bwd_ms), kernel="mmq_gemm_kernel<Q4_K, input gradient> (+ tile builder)",
-                                     traffic=MEASURED_DRAM_TRAFFIC.get("bwd"))
-        result["device_status"] = status
-        if rank == 0 and not args.no_cpu_baseline:
-            cpu = cpu_reference_arm(wl, steps=1, warmup=1)
-            result["cpu_baseline"] = {"value": cpu["value"], "unit": "TFLOP/s", "cores": cpu["cores"], "kind": "port",
-                                      "sample": cpu["sample"]}
-        parallelism = "single GPU"
+                                     traffic=MEASURED_DRAM_TRAFFIC.get("bwd"), traffic_source=MEASURED_DRAM_TRAFFIC["source"])
+        executor = "one GPU: grouped operators on expert-sorted rows resident in HBM"
     else:
-        # ---------------------------------------------------------------- expert parallel
-        w_local = w  # already the local shard [EL, N, row_bytes]
-        pep = None
-        if args.exchange == "peer":
-            from torch_ggml_ops_b200.peer_parallel import PeerExpertParallel
-
-            # The tokens of a rank are processed as `--micro` micro-batches, each with its own
-            # receive buffers and stream, so the NVLink exchange of one overlaps the matmuls of the
-            # other.  Receive buffers are sized for twice the mean load (the routing is skewed).
-            nmb = max(1, args.micro)
-            mb_tok = T // nmb
-            peps = [PeerExpertParallel(w_local, qt, E, N, K, capacity_rows=2 * mb_tok * top_k,
-                                       tokens_per_rank=mb_tok if args.token_level else None, top_k=top_k)
-                    for _ in range(nmb)]
-            pep = peps[0]
-            mb_streams = [torch.cuda.Stream() for _ in range(nmb)]
-            ids32 = ids.to(torch.int32)
-            mb_ids = [ids32[i * mb_tok:(i + 1) * mb_tok].contiguous() for i in range(nmb)]
-            mb_x = [x_tok[i * mb_tok:(i + 1) * mb_tok] for i in range(nmb)]
-            mb_dy = [dy_rows[i * mb_tok * top_k:(i + 1) * mb_tok * top_k] for i in range(nmb)]
-            y_all = torch.empty(R, N, dtype=torch.bfloat16, device=dev)
-            dx_all = torch.empty(T, K, dtype=torch.bfloat16, device=dev)
-            mb_y = [y_all[i * mb_tok * top_k:(i + 1) * mb_tok * top_k] for i in range(nmb)]
-            mb_dx = [dx_all[i * mb_tok:(i + 1) * mb_tok] for i in range(nmb)]
-
-        def step_peer():
-            # phases are issued round-robin over the micro-batches so that every rank enqueues its
-            # collectives (counts all-gather, fences) in the same order
-            cur = torch.cuda.current_stream()
-            for st in mb_streams:
-                st.wait_stream(cur)
-            plans = [None] * nmb
-            for i in range(nmb):
-                with torch.cuda.stream(mb_streams[i]):
-                    plans[i] = peps[i].plan(mb_ids[i])
-            for i in range(nmb):
-                with torch.cuda.stream(mb_streams[i]):
-                    peps[i].forward(plans[i], mb_x[i], out=mb_y[i])
-            for i in range(nmb):
-                with torch.cuda.stream(mb_streams[i]):
-                    peps[i].grad_input(plans[i], mb_dy[i], out=mb_dx[i])
-            for st in mb_streams:
-                cur.wait_stream(st)
-            return y_all, dx_all
-
-        def step_nccl():
-            plan = ep.plan(ids)
-            rows = ep.dispatch_tokens(plan, x_tok).requires_grad_(True)
-            out = tgo.grouped_mmq(rows, w_local, plan.expert_indices, plan.expert_offsets, qt, N)
-            y_back = ep.combine_rows(plan, out.detach())                 # forward result back at the token owner
-            dy_here = ep.dispatch_rows(plan, dy_rows)                    # cotangent to the expert owner
-            out.backward(dy_here)
-            dx_back = ep.combine_tokens(plan, rows.grad)                 # dX summed over the top-k slots
-            return y_back, dx_back
-
-        step_ep = step_peer if pep is not None else step_nccl
-
-        for _ in range(max(args.warmup, 3)):
-            step_ep()
-        barrier()
         sampler = ClockSampler(local_rank)
         sampler.start()
         keep_busy_for(1.0, step_ep)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        e0.record()
-        for _ in range(args.steps):
-            step_ep()
-        e1.record()
-        barrier()
+        ms_step = timed_steps(step_ep, args.steps)
         clocks = sampler.stop()
-        ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
-        # end to end with host buffers: tokens and cotangents come from pinned memory, results go back
-        xh, dyh = x_tok.cpu().pin_memory(), dy_rows.cpu().pin_memory()
-        yh = torch.empty(R, N, dtype=torch.bfloat16).pin_memory()
-        dxh = torch.empty(T, K, dtype=torch.bfloat16).pin_memory()
-
-        def step_e2e():
-            x_tok.copy_(xh, non_blocking=True)
-            dy_rows.copy_(dyh, non_blocking=True)
-            yb, dxb = step_ep()
-            yh.copy_(yb, non_blocking=True)
-            dxh.copy_(dxb, non_blocking=True)
-
-        for _ in range(3):
-            step_e2e()
-        barrier()
-        e0.record()
-        for _ in range(args.steps):
-            step_e2e()
-        e1.record()
-        barrier()
-        e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
-        h2d = xh.numel() * 2 + dyh.numel() * 2
-        d2h = yh.numel() * 2 + dxh.numel() * 2
         # this library's kernels per step: GEMMs + tile builders (4), routing sort (3), plan (2, + 1 for the
         # token maps), exchange (pair level 4; token level 6: dispatch, expand, pull y, dispatch dy, reduce, pull)
-        if pep is None:
-            launches = 4 + 3 + 6
-        else:
-            launches = (4 + 3 + (3 + 6 if args.token_level else 2 + 4)) * max(1, args.micro)
-        result["device_status"] = native.device_status()
-        if pep is not None:
-            result["ep_overflow"] = int(sum(int(q.overflow.item()) for q in peps))
-            result["micro_batches"] = nmb
-            parallelism = f"ep{world} (experts sharded; dispatch/combine by peer-memory kernels over NVLink, NCCL only for counts and fences)"
-        else:
-            parallelism = f"ep{world} (experts sharded, NCCL all-to-all dispatch/combine)"
+        launches = 4 + 3 + (3 + 6 if args.token_level else 2 + 4)
+        executor = (f"{world} GPUs: experts sharded; dispatch/combine by peer-memory kernels over NVLink, NCCL only for "
+                    "counts and fences")
+    result["device_status"] = native.device_status()
+    result["ep_overflow"] = int(pep.overflow.item())
+
+    # ---------------------------------------------------------------- parity on this rank's own results (not timed)
+    yb, dxb = step_ep()
+    torch.cuda.synchronize()
+    par = projection_parity(wl, seed, ids_cpu, x_tok, dy_rows, yb, dxb, args.parity_tokens)
+    par["fwd_rel_err"], par["dx_rel_err"] = max_over_ranks(par["fwd_rel_err"]), max_over_ranks(par["dx_rel_err"])
+    par["tolerance"] = {"fwd": 1e-2, "dx": 5e-3}
+    par["ranks_checked"] = world
+    result["parity"] = par
+
+    # ---------------------------------------------------------------- end to end with host buffers (every N)
+    # Tokens and per-pair cotangents come from pinned host memory, per-pair forward rows and
+    # per-token gradients go back to it, every step.  Three streams and two sets of device buffers:
+    # the copy-in of step i+1 and the copy-out of step i-1 overlap the work of step i.
+    xh, dyh = x_tok.cpu().pin_memory(), dy_rows.cpu().pin_memory()
+    yh = torch.empty(R, N, dtype=torch.bfloat16).pin_memory()
+    dxh = torch.empty(T, K, dtype=torch.bfloat16).pin_memory()
+    s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    xd = [torch.empty_like(x_tok) for _ in range(2)]
+    dyd = [torch.empty_like(dy_rows) for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_cmp = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+
+    def step_e2e(i):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_cmp[b])          # the step that last read these input buffers is done
+            xd[b].copy_(xh, non_blocking=True)
+            dyd[b].copy_(dyh, non_blocking=True)
+            ev_in[b].record(s_in)
+        with torch.cuda.stream(s_cmp):
+            s_cmp.wait_event(ev_in[b])
+            s_cmp.wait_event(ev_out[b])         # the copy-out that last read these output buffers is done
+            step_ep(xd[b], dyd[b], b)
+            ev_cmp[b].record(s_cmp)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_cmp[b])
+            yh.copy_(y_out[b], non_blocking=True)
+            dxh.copy_(dx_out[b], non_blocking=True)
+            ev_out[b].record(s_out)
+
+    def run_e2e(n):
+        for st in (s_in, s_cmp, s_out):
+            st.wait_stream(torch.cuda.current_stream())
+        for i in range(n):
+            step_e2e(i)
+        for st in (s_in, s_cmp, s_out):
+            torch.cuda.current_stream().wait_stream(st)
+
+    run_e2e(3)
+    e2e_ms = timed_steps(lambda: run_e2e(args.steps), 1) / args.steps
+    h2d = xh.numel() * 2 + dyh.numel() * 2
+    d2h = yh.numel() * 2 + dxh.numel() * 2
+    e2e = {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "numa_node": numa,
+           "form": "tokens + top-k ids + per-pair cotangents in, per-pair forward rows + per-token gradients out; "
+                   "routing sort, dispatch and combine inside the timed region"}
+
+    # ---------------------------------------------------------------- the expert-parallel MoE feed-forward configuration
+    if not args.no_config5:
+        result["config5"] = config5_step(args, world, rank, dev, seed, PeerMoEMLP, native, barrier, max_over_ranks, timed_steps)
+
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        cpu = cpu_reference_arm(wl, steps=1, warmup=1)
+        result["cpu_baseline"] = {"value": cpu["value"], "unit": "TFLOP/s", "cores": cpu["cores"], "kind": "port",
+                                  "sample": cpu["sample"]}
 
     if rank == 0:
         value = flops_step / (ms_step * 1e-3) / 1e12
@@ -474,23 +525,85 @@ def gpu_arm(args):
             "metric": "Q4_K grouped-MMQ fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl["name"], "quant": wl["quant"], "experts": E, "out_features": N, "in_features": K,
-                       "tokens_per_gpu": T, "top_k": top_k, "routed_rows_per_gpu": R, "parallelism": parallelism,
-                       "l2": "inputs larger than L2 (activations 268 MB + weights 151 MB per pass vs 126 MB L2)"},
+            "config": bench_config(wl, world), "executor": executor,
             "tokens_per_s": T * world / (ms_step * 1e-3),
-            "e2e": {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches * args.steps, "clocks": clocks,
+            "e2e": e2e, "gpu_launches": launches * args.steps, "clocks": clocks,
         }
         line.update(result)
         print(json.dumps(line))
+    failed = par["fwd_rel_err"] > 1e-2 or par["dx_rel_err"] > 5e-3
     if world > 1:
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit(f"parity check failed: {par}")
+
+
+def bench_config(wl, n_gpus):
+    """The `config` object: the workload, identical in both arms."""
+    return {"workload": wl["name"], "quant": wl["quant"], "experts": wl["experts"], "out_features": wl["N"],
+            "in_features": wl["K"], "tokens_per_gpu": wl["tokens"], "top_k": wl["top_k"],
+            "routed_rows_per_gpu": wl["tokens"] * wl["top_k"],
+            "parallelism": "single GPU" if n_gpus == 1 else f"ep{n_gpus}: experts sharded evenly, tokens data-parallel",
+            "l2": "inputs larger than L2 (activations 268 MB + weights 151 MB per pass vs 126 MB L2)"}
+
+
+CONFIG5 = {"name": "expert-parallel MoE feed-forward: 256 experts, IQ2_S gate/up 512 x 2048 + Q6_K down 2048 x 512, "
+                   "65536 tokens over all GPUs, top-8 Gaussian-logit routing, fwd + dX",
+           "experts": 256, "hidden": 2048, "ffn": 512, "tokens_total": 65536, "top_k": 8, "qt_gate_up": 22, "qt_down": 14}
+
+
+def config5_step(args, world, rank, dev, seed, PeerMoEMLP, native, barrier, max_over_ranks, timed_steps):
+    """BASELINE configuration 5: the whole MoE feed-forward step (gate/up pair, silu * up, down,
+    weighted combine; forward + input gradient) with the experts sharded over the GPUs and the
+    65536 tokens split evenly between them (strong scaling).  Returns its timing and parity."""
+    c5 = CONFIG5
+    E, H, F, top_k = c5["experts"], c5["hidden"], c5["ffn"], c5["top_k"]
+    T = c5["tokens_total"] // world
+    EL = E // world
+    lo, hi = rank * EL, (rank + 1) * EL
+    wg = torch.from_numpy(synthetic_expert_weights(c5["qt_gate_up"], E, F, H, seed + 1, lo, hi)).to(dev)
+    wu = torch.from_numpy(synthetic_expert_weights(c5["qt_gate_up"], E, F, H, seed + 2, lo, hi)).to(dev)
+    wd = torch.from_numpy(synthetic_expert_weights(c5["qt_down"], E, H, F, seed + 3, lo, hi)).to(dev)
+    ids_cpu = synthetic_routing(T, E, top_k, 2.0, seed + 100 + rank)
+    ids32 = torch.from_numpy(ids_cpu).to(dev).to(torch.int32)
+    gate_w = routing_weights(T, top_k, seed + 200 + rank)
+    gate_wd = gate_w.to(dev)
+    g = torch.Generator(device=dev).manual_seed(seed + 300 + rank)
+    x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    dy = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    rows = T * top_k
+    cap = rows if world == 1 else rows + rows // 2
+    mlp = PeerMoEMLP(wg, wu, wd, c5["qt_gate_up"], c5["qt_down"], E, H, F, capacity_rows=cap, tokens_per_rank=T, top_k=top_k)
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    dx = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+
+    def step():
+        mlp.plan(ids32, gate_wd)
+        mlp.forward(x, out=y)
+        mlp.grad_input(dy, out=dx)
+
+    for _ in range(3):
+        step()
+    steps = max(3, min(args.steps, 10))
+    ms = timed_steps(step, steps)
+    torch.cuda.synchronize()
+    par = mlp_parity(c5, seed, ids_cpu, gate_w, x, dy, y, dx, args.parity_tokens_mlp)
+    par["fwd_rel_err"], par["dx_rel_err"] = max_over_ranks(par["fwd_rel_err"]), max_over_ranks(par["dx_rel_err"])
+    par["tolerance"] = {"fwd": 1e-2, "dx": 1e-2, "note": "chain of three matmuls with bf16 results between them"}
+    overflow = int(mlp.r.plan["overflow"].item())
+    flops = 2 * 6.0 * F * H * c5["tokens_total"] * top_k     # gate + up + down, forward + input gradient
+    out = {"workload": c5["name"], "tokens_per_gpu": T, "steps": steps, "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+           "tokens_per_s": c5["tokens_total"] / (ms * 1e-3), "scaling": "strong", "parity": par, "ep_overflow": overflow,
+           "device_status": native.device_status()}
+    del mlp
+    if par["fwd_rel_err"] > 1e-2 or par["dx_rel_err"] > 1e-2:
+        raise SystemExit(f"MoE feed-forward parity check failed: {par}")
+    return out
 
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the GEMM kernel on this
-# workload, from the ncu capture summarised under profiles/; None until a capture exists.
-MEASURED_DRAM_TRAFFIC = {"fwd": 477.2e6, "bwd": 442.8e6}  # profiles/mmq_gemm_q4k_grouped_ncu_full.txt
+# workload, from the ncu capture summarised in the file named here; not measured by this run.
+MEASURED_DRAM_TRAFFIC = {"fwd": 477.2e6, "bwd": 442.8e6, "source": "profiles/mmq_gemm_q4k_grouped_ncu_full.txt"}
 
 
 def reference_arm(args):
@@ -498,14 +611,13 @@ def reference_arm(args):
     if rank != 0:
         return
     wl = WORKLOAD
-    cpu = cpu_reference_arm(wl, steps=max(1, min(args.steps, 3)), warmup=1)
+    steps, warmup = max(1, args.steps), max(1, min(args.warmup, 3))
+    cpu = cpu_reference_arm(wl, steps=steps, warmup=warmup)
     line = {
         "impl": "reference", "metric": "Q4_K grouped-MMQ fwd+bwd TFLOP/s", "value": cpu["value"], "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": max(1, min(args.steps, 3)), "warmup": 1, "ms_per_step": cpu["ms_per_step"],
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": cpu["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl["name"], "quant": wl["quant"], "experts": wl["experts"], "out_features": wl["N"],
-                   "in_features": wl["K"], "tokens_per_gpu": wl["tokens"], "top_k": wl["top_k"],
-                   "parallelism": "host CPU, all cores"},
+        "config": bench_config(wl, args.gpus), "executor": "host CPU, all cores (rank 0 only)",
         "cpu_baseline": {"value": cpu["value"], "unit": "TFLOP/s", "cores": cpu["cores"], "kind": "port",
                          "sample": cpu["sample"]},
         "e2e": {"value": cpu["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -590,10 +702,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--micro", type=int, default=1,
-                    help="multi-GPU peer exchange: micro-batches per step (exchange of one overlaps matmuls of another)")
-    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
-                    help="multi-GPU row exchange: this library's peer-memory kernels, or NCCL all-to-all")
+    ap.add_argument("--parity-tokens", type=int, default=32, help="tokens per rank checked against the oracle (not timed)")
+    ap.add_argument("--parity-tokens-mlp", type=int, default=6, help="tokens per rank checked in the MoE feed-forward step")
+    ap.add_argument("--no-config5", action="store_true", help="skip the expert-parallel MoE feed-forward configuration")
     ap.add_argument("--pair-level", dest="token_level", action="store_false",
                     help="multi-GPU peer exchange: move one row per routed pair instead of one per (token, destination GPU)")
     ap.add_argument("--profile", action="store_true",

@@ -201,7 +201,9 @@ int tgo_ep_pull(void* const* peer_ptrs, int64_t world, const int32_t* dst_rank, 
  *
  *  tgo_ep_token_maps      after tgo_ep_plan: writes, on every owner g, slot_rows[g][slot][s] (the row
  *                         of the slot's s-th routed pair on g, or -1; int32 [world*tokens_per_rank][top_k])
- *                         and, on the pair's owner, row_slot[owner][row] = slot (int32 [capacity]);
+ *                         and, on the pair's owner, row_slot[owner][row] = slot (int32 [capacity]) and, when
+ *                         pair_weights (fp32 [tokens * top_k]) is given, row_weight[owner][row] = the pair's
+ *                         routing weight (fp32 [capacity]; both null otherwise);
  *  tgo_ep_dispatch_tokens writes src[t] into the token buffer of every GPU that owns one of t's experts;
  *  tgo_ep_expand          owner side: rows[row] = token_buffer[row_slot[row]] for row < *n_rows_device
  *                         (a device int32, e.g. the last cumulative offset of tgo_ep_plan); a row whose
@@ -210,7 +212,8 @@ int tgo_ep_pull(void* const* peer_ptrs, int64_t world, const int32_t* dst_rank, 
  *  tgo_ep_pull_tokens     out[t] = sum over the GPUs owning one of t's experts of their partial_sums[slot]. */
 int tgo_ep_token_maps(const int32_t* dst_rank, const int32_t* dst_row, int64_t tokens, int64_t top_k,
                       int64_t my_rank, int64_t tokens_per_rank, void* const* row_slot_ptrs,
-                      void* const* slot_rows_ptrs, int64_t world, void* stream);
+                      void* const* slot_rows_ptrs, const float* pair_weights,
+                      void* const* row_weight_ptrs, int64_t world, void* stream);
 int tgo_ep_dispatch_tokens(const void* src, const int32_t* dst_rank, int64_t tokens, int64_t top_k,
                            int64_t width, int64_t my_rank, int64_t tokens_per_rank,
                            void* const* token_buffer_ptrs, int64_t world, void* stream);
@@ -222,6 +225,21 @@ int tgo_ep_reduce(const void* rows, const int32_t* slot_rows, int64_t n_slots, i
 int tgo_ep_pull_tokens(void* const* partial_sum_ptrs, int64_t world, const int32_t* dst_rank,
                        int64_t tokens, int64_t top_k, int64_t my_rank, int64_t tokens_per_rank,
                        void* out, int64_t width, void* stream);
+
+/* ---- element-wise step of the MoE feed-forward block between the grouped projections (the
+ * reference leaves activation and combine to its caller, README.md:3; csrc/mmq_hip.cu:1054-1193
+ * returns gate and up separately).  bf16 rows of `width` (a multiple of 8), fp32 arithmetic.
+ * row_scale (fp32 [rows], may be null = 1) is the routing weight of each expert-major row;
+ * n_rows_device (device int32, may be null) limits the work to the rows that exist. */
+
+/* out = row_scale * silu(gate) * up */
+int tgo_swiglu_fwd(const void* gate, const void* up, const float* row_scale, void* out, int64_t rows,
+                   int64_t width, const int32_t* n_rows_device, void* stream);
+
+/* dgate = dh * row_scale * up * silu'(gate),  dup = dh * row_scale * silu(gate) */
+int tgo_swiglu_bwd(const void* dh, const void* gate, const void* up, const float* row_scale,
+                   void* dgate, void* dup, int64_t rows, int64_t width,
+                   const int32_t* n_rows_device, void* stream);
 
 /* Grouped forward for callers that cannot hand over a workspace and must not trigger a device
  * allocation: the same operation and results as tgo_grouped_fwd, with the tile list kept in a

@@ -138,3 +138,34 @@ def test_single_rank_wrapper(cuda, token_level):
     assert ref.rel_frobenius(y.float().cpu(), want_y) < FWD_TOL
     assert ref.rel_frobenius(dx.float().cpu(), want_dx) < DX_TOL
     assert int(pep.overflow.item()) == 0
+    pep.check_overflow()
+    if token_level:
+        with pytest.raises(ValueError, match="top_k"):   # every rank must take the same exchange form
+            pep.plan(to_dev(torch.from_numpy(ids[:, :1].copy())))
+
+
+def test_overflow_is_surfaced_by_the_wrapper(cuda):
+    from torch_ggml_ops_b200.peer_parallel import PeerExpertParallel
+
+    qt, E, N, K, tokens, top_k = ref.Q4_K, 4, 64, 256, 64, 2
+    w = blocks.expert_weights(qt, E, N, K, 4)
+    W = torch.from_numpy(ref.expert_weights_fp32(w, qt, N, K))
+    ids = blocks.topk_routing(tokens, E, top_k, seed=1)
+    x = blocks.gaussian_bf16((tokens, K), 5)
+    pep = PeerExpertParallel(to_dev(w), qt, E, N, K, capacity_rows=48)      # 128 routed pairs do not fit
+    plan = pep.plan(to_dev(torch.from_numpy(ids)))
+    y = pep.forward(plan, to_dev(x))
+    with pytest.raises(RuntimeError, match="overflow"):
+        pep.check_overflow()
+    # the pairs that fitted are computed (also those of the expert that straddles the capacity), the rest are zeros
+    kept = plan["dst_rank"].cpu().numpy() >= 0
+    assert kept.sum() == 48
+    f = ids.reshape(-1)
+    want = torch.stack([x[i // top_k].float() @ W[f[i]].t() for i in range(f.size)])
+    got = y.float().cpu()
+    assert ref.rel_frobenius(got[kept], want[kept]) < FWD_TOL
+    assert int(torch.count_nonzero(got[~kept])) == 0
+    # the flag describes the last plan only
+    pep2_ids = to_dev(torch.from_numpy(ids[:20].copy()))
+    pep.plan(pep2_ids)
+    pep.check_overflow()

@@ -153,7 +153,9 @@ __global__ void __launch_bounds__(256) ep_pull_kernel(const __grid_constant__ Pe
 __global__ void __launch_bounds__(256) ep_token_maps_kernel(const int32_t* __restrict__ dst_rank, const int32_t* __restrict__ dst_row,
                                                             long long n_pairs, int top_k, int world, long long slot0,
                                                             const __grid_constant__ PeerPtrs row_slot,
-                                                            const __grid_constant__ PeerPtrs slot_rows) {
+                                                            const __grid_constant__ PeerPtrs slot_rows,
+                                                            const float* __restrict__ pair_weights,
+                                                            const __grid_constant__ PeerPtrs row_weight) {
     const long long i = blockIdx.x * 256LL + threadIdx.x;
     if (i >= n_pairs) return;
     const long long t = i / top_k;
@@ -161,7 +163,11 @@ __global__ void __launch_bounds__(256) ep_token_maps_kernel(const int32_t* __res
     const int r = dst_rank[i], row = dst_row[i];
     const long long slot = slot0 + t;
     for (int g = 0; g < world; ++g) static_cast<int32_t*>(slot_rows.p[g])[slot * top_k + s] = (r == g) ? row : -1;
-    if (r >= 0) static_cast<int32_t*>(row_slot.p[r])[row] = static_cast<int32_t>(slot);
+    if (r >= 0) {
+        static_cast<int32_t*>(row_slot.p[r])[row] = static_cast<int32_t>(slot);
+        // the pair's routing weight travels with the map, so the owner can scale the row it computes
+        if (pair_weights != nullptr) static_cast<float*>(row_weight.p[r])[row] = pair_weights[i];
+    }
 }
 
 // tok[g][slot][:] = src[t][:] for every GPU g that owns at least one of token t's experts.
@@ -343,19 +349,23 @@ int tgo_ep_pull(void* const* peer_ptrs, int64_t world, const int32_t* dst_rank, 
 }
 
 int tgo_ep_token_maps(const int32_t* dst_rank, const int32_t* dst_row, int64_t tokens, int64_t top_k, int64_t my_rank,
-                      int64_t tokens_per_rank, void* const* row_slot_ptrs, void* const* slot_rows_ptrs, int64_t world,
-                      void* stream) {
+                      int64_t tokens_per_rank, void* const* row_slot_ptrs, void* const* slot_rows_ptrs,
+                      const float* pair_weights, void* const* row_weight_ptrs, int64_t world, void* stream) {
     if (dst_rank == nullptr || dst_row == nullptr) return route_fail(TGO_E_ARG, "null pointer");
     if (tokens <= 0 || top_k <= 0 || top_k > 1024 || tokens > tokens_per_rank || my_rank < 0 || my_rank >= world ||
         tokens_per_rank * world * top_k > INT32_MAX)
         return route_fail(TGO_E_ARG, "token maps need 0 < tokens <= tokens_per_rank, 0 < top_k <= 1024 and the rank inside the world");
-    PeerPtrs rs = {}, sr = {};
+    if ((pair_weights == nullptr) != (row_weight_ptrs == nullptr))
+        return route_fail(TGO_E_ARG, "pair_weights and row_weight_ptrs must both be given or both be null");
+    PeerPtrs rs = {}, sr = {}, rw = {};
     int rc = fill_peers(rs, row_slot_ptrs, world);
     if (rc == TGO_OK) rc = fill_peers(sr, slot_rows_ptrs, world);
+    if (rc == TGO_OK && row_weight_ptrs != nullptr) rc = fill_peers(rw, row_weight_ptrs, world);
     if (rc != TGO_OK) return rc;
     const long long n_pairs = tokens * top_k;
     ep_token_maps_kernel<<<static_cast<int>((n_pairs + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        dst_rank, dst_row, n_pairs, static_cast<int>(top_k), static_cast<int>(world), my_rank * tokens_per_rank, rs, sr);
+        dst_rank, dst_row, n_pairs, static_cast<int>(top_k), static_cast<int>(world), my_rank * tokens_per_rank, rs, sr,
+        pair_weights, rw);
     return ep_launch_check("ep_token_maps_kernel launch failed");
 }
 

@@ -37,7 +37,9 @@ SIGNATURES = {
     "tgo_ep_plan": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tgo_ep_dispatch": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _vp, _i64, _vp]),
     "tgo_ep_pull": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
-    "tgo_ep_token_maps": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp]),
+    "tgo_ep_token_maps": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "tgo_swiglu_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp]),
+    "tgo_swiglu_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "tgo_ep_dispatch_tokens": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tgo_ep_expand": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp]),
     "tgo_ep_reduce": (_i32, [_vp, _vp, _i64, _i64, _vp, _i64, _vp]),
@@ -245,12 +247,26 @@ def ep_pull(peer_ptrs, dst_rank, dst_row, out, group=1, weights=None, stream=Non
 
 
 def ep_token_maps(dst_rank, dst_row, tokens, top_k, my_rank, tokens_per_rank, row_slot_ptrs, slot_rows_ptrs,
-                  stream=None) -> None:
+                  stream=None, pair_weights=None, row_weight_ptrs=None) -> None:
     """Token-level exchange, plan time: per-slot row lists on every owner and the row -> slot map on
-    each pair's owner; see ``tgo_ep_token_maps``."""
+    each pair's owner (plus, with ``pair_weights`` fp32 [tokens * top_k], each row's routing weight
+    on its owner); see ``tgo_ep_token_maps``."""
     check(lib().tgo_ep_token_maps(_ptr(dst_rank), _ptr(dst_row), tokens, top_k, my_rank, tokens_per_rank,
-                                  _ptr_array(row_slot_ptrs), _ptr_array(slot_rows_ptrs), len(row_slot_ptrs),
-                                  _stream(stream)), "tgo_ep_token_maps")
+                                  _ptr_array(row_slot_ptrs), _ptr_array(slot_rows_ptrs), _ptr(pair_weights),
+                                  None if row_weight_ptrs is None else _ptr_array(row_weight_ptrs),
+                                  len(row_slot_ptrs), _stream(stream)), "tgo_ep_token_maps")
+
+
+def swiglu_fwd(gate, up, out, row_scale=None, n_rows_device=None, stream=None) -> None:
+    """out = row_scale * silu(gate) * up on bf16 rows (``tgo_swiglu_fwd``)."""
+    check(lib().tgo_swiglu_fwd(_ptr(gate), _ptr(up), _ptr(row_scale), _ptr(out), gate.shape[0], gate.shape[1],
+                               _ptr(n_rows_device), _stream(stream)), "tgo_swiglu_fwd")
+
+
+def swiglu_bwd(dh, gate, up, dgate, dup, row_scale=None, n_rows_device=None, stream=None) -> None:
+    """dgate, dup of ``swiglu_fwd`` for the cotangent ``dh`` (``tgo_swiglu_bwd``)."""
+    check(lib().tgo_swiglu_bwd(_ptr(dh), _ptr(gate), _ptr(up), _ptr(row_scale), _ptr(dgate), _ptr(dup), gate.shape[0],
+                               gate.shape[1], _ptr(n_rows_device), _stream(stream)), "tgo_swiglu_bwd")
 
 
 def ep_dispatch_tokens(src, dst_rank, top_k, my_rank, tokens_per_rank, token_buffer_ptrs, stream=None) -> None:
