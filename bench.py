@@ -603,7 +603,7 @@ def config5_step(args, world, rank, dev, seed, PeerMoEMLP, native, barrier, max_
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the GEMM kernel on this
 # workload, from the ncu capture summarised in the file named here; not measured by this run.
-MEASURED_DRAM_TRAFFIC = {"fwd": 477.2e6, "bwd": 442.8e6, "source": "profiles/mmq_gemm_q4k_grouped_ncu_full.txt"}
+MEASURED_DRAM_TRAFFIC = {"fwd": 475.9e6, "bwd": 442.8e6, "source": "profiles/mmq_gemm_q4k_grouped_ncu_full.txt"}
 
 
 def reference_arm(args):
@@ -670,6 +670,18 @@ def sweep_arm(args):
         f = timed(lambda: native.mmq_fwd(x, w, y, M, N, K, qt), args.steps)
         b = timed(lambda: native.mmq_dx(dy, w, dx, M, N, K, qt), args.steps)
         report(f"dense {names[qt]} M={M} N={N} K={K}", 2.0 * M * N * K, f, b)
+
+    # the LM-head shape of the reference's chunked loss loop (docs/mmq_bwd_optimization.md:442-446, 502-524)
+    V, Kh = 248320, 2048
+    wh = torch.from_numpy(synthetic_expert_weights(14, 1, V, Kh, 12)).to(dev)[0]
+    for M in (64, 128, 256):
+        x, dy = bf16(M, Kh, 1), bf16(M, V, 2)
+        y = torch.empty(M, V, dtype=torch.bfloat16, device=dev)
+        dx = torch.empty(M, Kh, dtype=torch.bfloat16, device=dev)
+        f = timed(lambda: native.mmq_fwd(x, wh, y, M, V, Kh, 14), args.steps)
+        b = timed(lambda: native.mmq_dx(dy, wh, dx, M, V, Kh, 14), args.steps)
+        report(f"LM head Q6_K M={M} N={V} K={Kh} (weight 417 MB read per call)", 2.0 * M * V * Kh, f, b)
+    del wh
 
     def grouped(qt, E, N, K, tokens, top_k, pair, label):
         ids = synthetic_routing(tokens, E, top_k, 2.0, 2024)

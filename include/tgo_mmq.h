@@ -87,6 +87,17 @@ int tgo_mmq_fwd(const void* x, const void* packed_weight, void* y, int64_t rows,
 int tgo_mmq_dx(const void* dy, const void* packed_weight, void* dx, int64_t rows,
                int64_t out_features, int64_t in_features, int quant_type, void* stream);
 
+/* Several dense projections of the same activations in one call: ys[i] = X * W_i^T for
+ * num_weights (1..4) packed weights of the same quant type and shape [out_features, in_features];
+ * packed_weights and ys are HOST arrays of device pointers.  Two weight sets share a launch, as the
+ * gate/up pair does in tgo_grouped_fwd; every ys[i] is bit-identical to tgo_mmq_fwd on W_i alone.
+ * No counterpart in the reference, which lists a dense pair / multi-projection operator as its
+ * remaining dense-forward work (docs/mmq_fwd_optimization.md:299-307: there the shared cost is the
+ * q8_1 quantisation of the activations, which this library's bf16 path does not have at all). */
+int tgo_mmq_fwd_multi(const void* x, const void* const* packed_weights, void* const* ys,
+                      int64_t num_weights, int64_t rows, int64_t out_features, int64_t in_features,
+                      int quant_type, void* stream);
+
 /* Workspace bytes the grouped calls below need for `rows` routed rows in `num_groups` groups
  * (the device-built tile list; reference: new_grouped_row_task_workspace,
  * csrc/mmq_hip.cu:544-558). */

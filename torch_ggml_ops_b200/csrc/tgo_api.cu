@@ -657,6 +657,23 @@ int tgo_mmq_dx(const void* dy, const void* packed_weight, void* dx, int64_t rows
     return run_problem(p, static_cast<cudaStream_t>(stream));
 }
 
+int tgo_mmq_fwd_multi(const void* x, const void* const* packed_weights, void* const* ys, int64_t num_weights, int64_t rows,
+                      int64_t out_features, int64_t in_features, int quant_type, void* stream) {
+    if (packed_weights == nullptr || ys == nullptr) return fail(TGO_E_ARG, "null pointer array");
+    if (num_weights < 1 || num_weights > 4) return fail(TGO_E_ARG, "num_weights must be in 1..4; got %lld", (long long)num_weights);
+    // one launch covers two weight sets (their tiles share the launch and the activation rows' L2 residency)
+    for (int64_t s = 0; s < num_weights; s += 2) {
+        Problem p = {};
+        p.nsets = num_weights - s >= 2 ? 2 : 1;
+        p.act[0] = x;
+        for (int i = 0; i < p.nsets; ++i) { p.wgt[i] = packed_weights[s + i]; p.out[i] = ys[s + i]; }
+        p.rows = rows; p.N = out_features; p.K = in_features; p.E = 1; p.qt = quant_type; p.mode = kFwd;
+        const int rc = run_problem(p, static_cast<cudaStream_t>(stream));
+        if (rc != TGO_OK) return rc;
+    }
+    return TGO_OK;
+}
+
 int64_t tgo_grouped_workspace_bytes(int64_t rows, int64_t num_groups) {
     if (rows < 0 || num_groups < 0) return -1;
     return 16 + 16 * task_capacity(rows, num_groups);

@@ -25,6 +25,7 @@ SIGNATURES = {
     "tgo_dequantize_bf16": (_i32, [_vp, _i64, _i32, _vp, _vp]),
     "tgo_mmq_fwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "tgo_mmq_dx": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "tgo_mmq_fwd_multi": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tgo_grouped_workspace_bytes": (_i64, [_i64, _i64]),
     "tgo_build_tiles": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tgo_grouped_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
@@ -121,6 +122,13 @@ def mmq_fwd(x, packed, y, rows, out_features, in_features, quant_type, stream=No
 def mmq_dx(dy, packed, dx, rows, out_features, in_features, quant_type, stream=None) -> None:
     check(lib().tgo_mmq_dx(_ptr(dy), _ptr(packed), _ptr(dx), rows, out_features, in_features, quant_type,
                            _stream(stream)), "tgo_mmq_dx")
+
+
+def mmq_fwd_multi(x, packed_list, y_list, rows, out_features, in_features, quant_type, stream=None) -> None:
+    """ys[i] = x @ W_i.T for up to four packed weights of one type and shape (``tgo_mmq_fwd_multi``)."""
+    check(lib().tgo_mmq_fwd_multi(_ptr(x), _ptr_array([w.data_ptr() for w in packed_list]),
+                                  _ptr_array([y.data_ptr() for y in y_list]), len(packed_list), rows, out_features,
+                                  in_features, quant_type, _stream(stream)), "tgo_mmq_fwd_multi")
 
 
 def grouped_workspace_bytes(rows: int, groups: int) -> int:
