@@ -646,6 +646,20 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
 
         // waits until this step's decoded-weight slot is free, decodes into it and signals the step
         auto emit = [&](uint32_t blk, int g, bool valid, uint32_t raw_bar_to_release) -> bool {
+            // Decode first, into registers: the arithmetic does not need the destination slot, so
+            // it overlaps the wait for that slot, and what follows the wait (four stores, a fence,
+            // an arrival) is short.  The slot's credit loop - the latency that sets the stage time -
+            // no longer contains the decode.
+            uint4 o[4];
+            if (valid) {
+                decode32<QT>(blk, g, grid_s, o);
+            } else {
+                o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (raw_bar_to_release != 0) {   // the raw blocks are in registers now: hand the raw stage back early
+                __syncwarp();
+                if (lane == 0) mbar_arrive(raw_bar_to_release);
+            }
             // Without wide tiles every pipeline stage is KS consecutive steps, so the stages and the
             // slot follow from the step index alone; with them they are the running values above.
             const uint32_t stg_now = WIDE ? stg : it / KS;
@@ -654,12 +668,6 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 if (WIDE) j = (it - d0 >= static_cast<uint32_t>(NAS)) ? static_cast<uint32_t>(jw) : last_reader(it - NAS);
                 else j = (it - NAS) / KS;
                 if (!all_wait(bar_done + 8 * (j % NB), (j / NB) & 1u, abort_word, kAbortWgtEmpty)) return false;
-            }
-            uint4 o[4];
-            if (valid) {
-                decode32<QT>(blk, g, grid_s, o);
-            } else {
-                o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
             }
             const uint32_t tile_s = wgt_s + (WIDE ? slot_off : (it % NAS) * kWgtTileBytes);
 #pragma unroll
@@ -671,7 +679,6 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 if (WIDE && wide) {   // the second half reads this step in the next pipeline stage
                     if (CG == 2) mbar_arrive_cluster(lead_full + 8 * ((stg_now + 1u) % NB)); else mbar_arrive(bar_full + 8 * ((stg_now + 1u) % NB));
                 }
-                if (raw_bar_to_release != 0) mbar_arrive(raw_bar_to_release);
             }
             it += kDecodeGroups;
             if (WIDE) {
