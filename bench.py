@@ -679,8 +679,8 @@ def sweep_arm(args):
         y = torch.empty(M, V, dtype=torch.bfloat16, device=dev)
         dx = torch.empty(M, Kh, dtype=torch.bfloat16, device=dev)
         f = timed(lambda: native.mmq_fwd(x, wh, y, M, V, Kh, 14), args.steps)
-        b = timed(lambda: native.mmq_dx(dy, wh, dx, M, V, Kh, 14), args.steps)
-        report(f"LM head Q6_K M={M} N={V} K={Kh} (weight 417 MB read per call)", 2.0 * M * V * Kh, f, b)
+        b = timed(lambda: native.mmq_dx_split(dy, wh, dx, M, V, Kh, 14), args.steps)
+        report(f"LM head Q6_K M={M} N={V} K={Kh} (weight 417 MB read per call; dX with the split reduction)", 2.0 * M * V * Kh, f, b)
     del wh
 
     def grouped(qt, E, N, K, tokens, top_k, pair, label):

@@ -87,6 +87,20 @@ int tgo_mmq_fwd(const void* x, const void* packed_weight, void* y, int64_t rows,
 int tgo_mmq_dx(const void* dy, const void* packed_weight, void* dx, int64_t rows,
                int64_t out_features, int64_t in_features, int quant_type, void* stream);
 
+/* Dense input gradient with a workspace for the split reduction.  When the problem has few tiles
+ * and a long reduction (few rows, very many out-features: an LM head of 248320 x 2048 gives 8 tiles
+ * of 3880 steps) the out-features are cut into ranges, one tile each, whose fp32 partial sums go to
+ * `workspace` and are added in ascending order by a second kernel; results then differ from
+ * tgo_mmq_dx only by that summation order.  tgo_mmq_dx_workspace_bytes returns the bytes needed on
+ * the current device (0: no split, and tgo_mmq_dx_ws is tgo_mmq_dx).  Replaces the small-M dispatch
+ * of ck::launch_dense_mmq_grad_input (csrc/ck/mmq_backward.cuh:1066-1241), which picks narrower
+ * tiles for the same reason; shapes: docs/mmq_bwd_optimization.md:442-446. */
+int64_t tgo_mmq_dx_workspace_bytes(int64_t rows, int64_t out_features, int64_t in_features,
+                                   int quant_type);
+int tgo_mmq_dx_ws(const void* dy, const void* packed_weight, void* dx, int64_t rows,
+                  int64_t out_features, int64_t in_features, int quant_type, void* workspace,
+                  int64_t workspace_bytes, void* stream);
+
 /* Several dense projections of the same activations in one call: ys[i] = X * W_i^T for
  * num_weights (1..4) packed weights of the same quant type and shape [out_features, in_features];
  * packed_weights and ys are HOST arrays of device pointers.  Two weight sets share a launch, as the

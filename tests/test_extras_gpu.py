@@ -105,7 +105,9 @@ def test_chunked_lm_head_loss(cuda):
 
     qt, V, K, T = ref.Q6_K, 1000, 512, 600
     w, W, _ = dense_case(qt, V, K, 8)
-    hidden = blocks.gaussian_bf16((T, K), 9)
+    # hidden states scaled so that the logits have a spread of about one (with a spread of 60 the
+    # softmax is so peaked that the bf16 rounding of the logits alone moves the gradient by 3 %)
+    hidden = (blocks.gaussian_bf16((T, K), 9).float() * 0.02).to(torch.bfloat16)
     targets = torch.from_numpy(np.random.default_rng(1).integers(0, V, size=T))
     loss, dh = tgo.lm_head_loss(to_dev(hidden), to_dev(w), qt, V, to_dev(targets), chunk_rows=256)
     hf = hidden.double().requires_grad_(True)
@@ -118,3 +120,32 @@ def test_chunked_lm_head_loss(cuda):
     loss64, dh64 = tgo.lm_head_loss(to_dev(hidden), to_dev(w), qt, V, to_dev(targets), chunk_rows=64)
     assert abs(float(loss64) - float(loss)) / float(want) < 1e-4
     assert ref.rel_frobenius(dh64.float().cpu(), dh.float().cpu()) < 1e-3
+
+
+@pytest.mark.parametrize("name,qt", ALL_TYPES)
+@pytest.mark.parametrize("M,N,K", [(100, 8192, 512), (256, 8200, 256), (37, 8201, 512)])
+def test_split_reduction_of_the_dense_input_gradient(cuda, name, qt, M, N, K):
+    """Few rows against very many out-features: the reduction is cut into ranges with fp32 partial
+    sums (the LM-head shape).  Same result as the unsplit launch up to the summation order, within
+    the input-gradient tolerance of the oracle, row by row; N = 8200 leaves the last range part
+    empty, N = 8201 takes the plain-load activation path (rows of 16402 bytes)."""
+    from torch_ggml_ops_b200 import native
+
+    w, W, _ = dense_case(qt, N, K, 90 + qt)
+    dy = blocks.gaussian_bf16((M, N), 4)
+    dyd, wd = to_dev(dy), to_dev(w)
+    plain = torch.full((M, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+    split = torch.full((M, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+    native.mmq_dx(dyd, wd, plain, M, N, K, qt)
+    used = native.mmq_dx_split(dyd, wd, split, M, N, K, qt)
+    torch.cuda.synchronize()
+    assert used > 0 and used % (M * K * 4) == 0 and used // (M * K * 4) >= 2     # it did split
+    want = ref.mmq_grad_input(dy, W)
+    assert not torch.isnan(split).any()
+    assert ref.rel_frobenius(split.float().cpu(), want) < DX_TOL
+    assert ref.max_row_error(split.float().cpu(), want) < 2 * DX_TOL
+    assert ref.rel_frobenius(split.float().cpu(), plain.float().cpu()) < 3e-3
+    # the torch operator takes the same path on its own
+    op = torch.ops.torch_ggml_ops.mmq_grad_input(dyd, wd, qt, K)
+    assert np.array_equal(bits(op), bits(split))
+    assert native.device_status() == 0

@@ -137,6 +137,12 @@ struct GemmArgs {
     int wgt_classes;                     // P: alignment classes of the packed weight rows (1, 2, 4 or 8)
     int wgt_classes_log2;
     int wgt_row_bytes;                   // (K / 256) * block bytes
+    // Split reduction (dense input gradient with few tiles and a long reduction): the out-features
+    // are cut into nsplit ranges of split_steps 64-element steps, each tile reduces one range and
+    // writes fp32 partial sums [split][row][k] to `partial`; a second kernel adds them in order.
+    float* partial;                      // null: no split
+    int nsplit;                          // 1: no split
+    int split_steps;                     // steps per split (a multiple of the steps per stage)
 };
 
 // CG = 1: one CTA per tile of 128 weight rows.  CG = 2: a cluster of two CTAs works on 256 weight
@@ -191,6 +197,7 @@ struct GemmCfg {
 
 struct TileInfo {
     int expert, row0, ntok, set, m0;
+    int split;   // backward with a split reduction: which range of the out-features
     int nhalf;   // 1, or 2 for a wide tile (more than kTileTok tokens)
     int tok0;    // tokens of half 0; half 1 holds the other ntok - tok0
 };
@@ -227,11 +234,13 @@ __device__ __forceinline__ bool load_tile(const GemmArgs& a, int tile, int mtile
         t.tok0 = t.ntok;
     }
     if (MODE == kFwd) {
+        t.split = 0;
         t.set = mt / mtiles_set;
         t.m0 = ((mt - t.set * mtiles_set) * CG + rank) * kTileM;
     } else {
         t.set = 0;
-        t.m0 = (mt * CG + rank) * kTileM;
+        t.split = mt / mtiles_set;                      // 0 unless the reduction is split
+        t.m0 = ((mt - t.split * mtiles_set) * CG + rank) * kTileM;
     }
     return t.ntok > 0;
 }
@@ -303,9 +312,13 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     const int nkb = K >> 8;
     // tile space
     const int mtiles_set = MODE == kFwd ? (N + CG * kTileM - 1) / (CG * kTileM) : K / (CG * kTileM);
-    const int mtiles = MODE == kFwd ? mtiles_set * args.nsets : mtiles_set;
+    const int nsplit = MODE == kBwd ? args.nsplit : 1;
+    const int mtiles = MODE == kFwd ? mtiles_set * args.nsets : mtiles_set * nsplit;
     const int steps_set = MODE == kFwd ? K / kStepK : (N + kStepK - 1) / kStepK;
-    const int nsteps = MODE == kFwd ? steps_set : steps_set * args.nsets;   // 64-element steps of a tile
+    // 64-element steps of a tile: the whole reduction (both weight sets of a pair backward), or one
+    // range of it when the reduction is split
+    const int nsteps = MODE == kFwd ? steps_set : (nsplit > 1 ? args.split_steps : steps_set * args.nsets);
+    const int steps_all = MODE == kFwd ? steps_set : steps_set * args.nsets;   // steps that hold data
     const int nstages = (nsteps + KS - 1) / KS;                              // decoded stages of a tile
     const int nsteps_pad = nstages * KS;   // a stage's missing steps are fed zeros
     const int ntasks = args.tasks != nullptr ? *args.task_count : args.dense_tasks;
@@ -380,10 +393,11 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
 #pragma unroll
                         for (int ks = 0; ks < KS; ++ks) {
                             const int step = stage * KS + ks;
-                            int set = MODE == kFwd ? 0 : step / steps_set;
+                            const int astep = MODE == kFwd ? step : t.split * nsteps + step;   // step of the whole reduction
+                            int set = MODE == kFwd ? 0 : astep / steps_set;
                             // a step past the end reads columns outside the matrix: TMA fills zeros
-                            int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
-                            if (step >= nsteps) { set = 0; red0 = (steps_set + (step - nsteps)) * kStepK; }
+                            int red0 = (MODE == kFwd ? step : astep - set * steps_set) * kStepK;
+                            if (step >= nsteps || astep >= steps_all) { set = 0; red0 = (steps_set + 1) * kStepK; }
                             uint32_t dst = act_s + ((it * KS + ks) % NBS) * kActTileBytes;
                             int rem = hpad / CG;
                             int row = half_row0(t, half) + rank * rem;
@@ -425,9 +439,10 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     }
                     for (int ks = 0; ks < KS; ++ks) {
                         const int step = stage * KS + ks;
-                        int set = MODE == kFwd ? 0 : step / steps_set;
-                        int red0 = (MODE == kFwd ? step : step - set * steps_set) * kStepK;
-                        if (step >= nsteps) { set = 0; red0 = red_total; }   // a step past the end: zeros
+                        const int astep = MODE == kFwd ? step : t.split * nsteps + step;
+                        int set = MODE == kFwd ? 0 : astep / steps_set;
+                        int red0 = (MODE == kFwd ? step : astep - set * steps_set) * kStepK;
+                        if (step >= nsteps || astep >= steps_all) { set = 0; red0 = red_total; }   // a step past the end: zeros
                         const __nv_bfloat16* src = args.act[set];
                         uint8_t* dst = act_g + ((it * KS + ks) % NBS) * kActTileBytes;
                         for (int idx = lane; idx < my_rows * 8; idx += 32) {
@@ -568,8 +583,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     if (MODE == kFwd) {
                         set = t.set; n_first = t.m0; kb = ri;
                     } else {
-                        set = ri / steps_set; n_first = (ri - set * steps_set) * kStepK; kb = t.m0 >> 8;
-                        if (ri >= nsteps) { set = 0; n_first = 0; }   // a step past the end: decoded as zeros
+                        const int astep = t.split * nsteps + ri;
+                        set = astep / steps_set; n_first = (astep - set * steps_set) * kStepK; kb = t.m0 >> 8;
+                        if (ri >= nsteps || astep >= steps_all) { set = 0; n_first = 0; }   // a step past the end: decoded as zeros
                     }
                     const long long g0 = static_cast<long long>(t.expert) * N + n_first;  // first global weight row
                     const uint32_t bar = bar_raw_full + 8 * r;
@@ -739,8 +755,9 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     const uint32_t ri = d0 + step;
                     const uint32_t r = ri % NR, rph = (ri / NR) & 1u;
                     if (!all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull)) { ok = false; break; }
-                    const int n_first = (step >= steps_set ? step - steps_set : step) * kStepK;
-                    const bool valid = step < nsteps && n_first + row < N;
+                    const int astep = t.split * nsteps + step;
+                    const int n_first = (astep >= steps_set ? astep - steps_set : astep) * kStepK;
+                    const bool valid = step < nsteps && astep < steps_all && n_first + row < N;
                     if (!emit(blk0 + r * Cfg::kRawStageBytes, g, valid, bar_raw_empty + 8 * r)) { ok = false; break; }
                 }
             }
@@ -756,7 +773,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         const int ehalf = (warp - kFirstEpilogueWarp) >> 2;     // which of the alternate 16-token chunks
         const int mdim = MODE == kFwd ? N : K;
         // drains accumulator use `u` (rows row0 .. row0 + ntok of the output) and hands it back
-        auto drain = [&](uint32_t u, int m0, int set, int row0, int ntok) -> bool {
+        auto drain = [&](uint32_t u, int m0, int set, int row0, int ntok, int split) -> bool {
             const uint32_t acc = u & 1u, aph = (u >> 1) & 1u;
             const int ntok_pad = pad_tokens<CG>(ntok);
             if (!all_wait(bar_acc_full + 8 * acc, aph, abort_word, kAbortAccFull)) return false;
@@ -764,7 +781,21 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             const uint32_t taddr = tmem_base + acc * kTileTok + (static_cast<uint32_t>(quad * 32) << 16);
             const int mq = m0 + quad * 32;  // first output column of this warp
             __nv_bfloat16* out_base = args.out[MODE == kFwd ? set : 0] + static_cast<long long>(row0) * mdim;
-            if ((mdim & 7) == 0 && mq + 32 <= mdim) {
+            if (MODE == kBwd && args.partial != nullptr) {
+                // split reduction: fp32 partial sums, lane = output column (128 bytes per warp store)
+                const int m = mq + lane;
+                float* part = args.partial + (static_cast<long long>(split) * args.rows + row0) * mdim + m;
+                for (int c0 = 16 * ehalf; c0 < ntok_pad; c0 += 4 * kEpilogueWarps) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + c0, v);
+                    tmem_ld_wait();
+                    if (m < mdim) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < ntok) part[static_cast<long long>(c0 + j) * mdim] = __uint_as_float(v[j]);
+                    }
+                }
+            } else if ((mdim & 7) == 0 && mq + 32 <= mdim) {
                 // Transposing path: the warp's 32 outputs x 16 tokens go through a private staging
                 // tile [token][32 outputs] so that global stores are 16 bytes per lane.
                 uint8_t* stage = epi_g + (warp - kFirstEpilogueWarp) * (16 * 64);
@@ -814,10 +845,10 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         for (long long tile = cta; tile < total_tiles; tile += ncta) {
             TileInfo t;
             if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
-            if (!drain(tl, t.m0, t.set, t.row0, t.tok0)) break;
+            if (!drain(tl, t.m0, t.set, t.row0, t.tok0, t.split)) break;
             ++tl;
             if (WIDE && t.nhalf == 2) {   // the second half of a wide tile is an accumulator of its own
-                if (!drain(tl, t.m0, t.set, t.row0 + t.tok0, t.ntok - t.tok0)) break;
+                if (!drain(tl, t.m0, t.set, t.row0 + t.tok0, t.ntok - t.tok0, t.split)) break;
                 ++tl;
             }
         }

@@ -340,6 +340,21 @@ __global__ void __launch_bounds__(64) wait_selftest_kernel(long long limit_cycle
         atomicCAS(status, 0, abort_word | (static_cast<int>(blockIdx.x) << 8));
 }
 
+// ------------------------------------------------------------------ split-reduction epilogue
+// out[i] = bf16(sum over splits s, in ascending order, of partial[s][i]); four elements per thread.
+__global__ void __launch_bounds__(256) split_reduce_kernel(const float4* __restrict__ partial, int nsplit, long long n_vec,
+                                                           uint2* __restrict__ out) {
+    for (long long v = blockIdx.x * 256LL + threadIdx.x; v < n_vec; v += 256LL * gridDim.x) {
+        float4 acc = partial[v];
+        for (int s = 1; s < nsplit; ++s) {
+            const float4 p = partial[s * n_vec + v];
+            acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        }
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        out[v] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
+}
+
 // ------------------------------------------------------------------ GEMM dispatch
 static int dispatch_gemm(int qt, int mode, int cta_group, int wide, const GemmArgs& args, int grid, cudaStream_t stream) {
     int e;
@@ -403,6 +418,24 @@ static int check_status_if_asked(cudaStream_t stream) {
         return fail(TGO_E_DEVICE, "a kernel gave up a bounded wait: code %d in block %d (outputs of that launch are incomplete)",
                     v & 0xFF, v >> 8);
     return TGO_OK;
+}
+
+// Dense input gradient with few tiles and a long reduction (an LM head: 8 tiles of 3880 steps): the
+// out-features are cut into ranges so that every CTA pair gets a tile; each range's fp32 partial
+// sums go to a workspace and are added in a fixed order afterwards.  Returns the number of ranges
+// (1: no split) and the 64-element steps per range.
+static int plan_split(int64_t rows, int64_t N, int64_t K, int64_t tile_m, int64_t limit, int& split_steps) {
+    const int64_t tiles = ((rows + kTileTok - 1) / kTileTok) * (K / tile_m);
+    const int64_t steps = (N + kStepK - 1) / kStepK;
+    split_steps = 0;
+    if (tiles * 2 > limit || steps < 128) return 1;
+    int64_t s = limit / tiles;
+    if (s > steps / 32) s = steps / 32;          // at least 32 steps per range
+    if (s < 2) return 1;
+    int64_t per = (steps + s - 1) / s;
+    per = (per + 1) & ~1LL;                        // whole pipeline stages
+    split_steps = static_cast<int>(per);
+    return static_cast<int>((steps + per - 1) / per);
 }
 
 struct Problem {
@@ -501,7 +534,22 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
     const int wide_env = wide_tiles_env();
     bool wide = p.experts == nullptr && ((p.rows + kTileTok - 1) / kTileTok) * mtiles > limit;
     if (wide_env >= 0) wide = wide_env != 0;
-    const int max_tok = wide ? kWideTok : kTileTok;
+    int max_tok = wide ? kWideTok : kTileTok;
+    // split reduction: dense input gradient of a single weight with a workspace to hold the partial sums
+    int nsplit = 1, split_steps = 0;
+    if (p.experts == nullptr && p.mode == kBwd && p.nsets == 1 && p.ws != nullptr && wide_env < 0) {
+        nsplit = plan_split(p.rows, p.N, p.K, tile_m, limit, split_steps);
+        if (nsplit > 1) {
+            const int64_t need = static_cast<int64_t>(nsplit) * p.rows * p.K * 4;
+            if (p.ws_bytes < need) return fail(TGO_E_WORKSPACE, "workspace has %lld bytes, need %lld", (long long)p.ws_bytes, (long long)need);
+            if (!aligned16(p.ws)) return fail(TGO_E_ARG, "workspace pointer must be 16-byte aligned");
+            wide = false;
+            max_tok = kTileTok;
+        }
+    }
+    a.nsplit = nsplit;
+    a.split_steps = split_steps;
+    a.partial = nsplit > 1 ? static_cast<float*>(p.ws) : nullptr;
     int64_t max_tasks;
     if (p.experts == nullptr) {
         a.dense_tasks = static_cast<int>((p.rows + max_tok - 1) / max_tok);
@@ -515,7 +563,7 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
         a.tasks = reinterpret_cast<const int4*>(static_cast<const uint8_t*>(p.ws) + 16);
         max_tasks = cap;
     }
-    int64_t grid = max_tasks * mtiles;  // persistent CTAs (pairs) never outnumber the tiles
+    int64_t grid = max_tasks * mtiles * nsplit;  // persistent CTAs (pairs) never outnumber the tiles
     if (grid > limit) grid = limit;
     if (grid < 1) grid = 1;
     if (getenv("TGO_DEBUG_LAUNCH") != nullptr)
@@ -523,6 +571,15 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
                 (long long)(grid * cg), (long long)(max_tasks * mtiles));
     rc = dispatch_gemm(p.qt, p.mode, cg, wide ? 1 : 0, a, static_cast<int>(grid * cg), stream);
     if (rc != TGO_OK) return rc;
+    if (nsplit > 1) {
+        const long long n_vec = p.rows * p.K / 4;   // K is a multiple of 256
+        long long blocks = (n_vec + 255) / 256;
+        if (blocks > num_sms() * 8LL) blocks = num_sms() * 8LL;
+        split_reduce_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const float4*>(p.ws), nsplit, n_vec,
+                                                                          static_cast<uint2*>(p.out[0]));
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "split_reduce_kernel launch");
+    }
     return check_status_if_asked(stream);
 }
 
@@ -654,6 +711,28 @@ int tgo_mmq_dx(const void* dy, const void* packed_weight, void* dx, int64_t rows
     Problem p = {};
     p.act[0] = dy; p.wgt[0] = packed_weight; p.out[0] = dx; p.nsets = 1;
     p.rows = rows; p.N = out_features; p.K = in_features; p.E = 1; p.qt = quant_type; p.mode = kBwd;
+    return run_problem(p, static_cast<cudaStream_t>(stream));
+}
+
+int64_t tgo_mmq_dx_workspace_bytes(int64_t rows, int64_t out_features, int64_t in_features, int quant_type) {
+    if (rows <= 0 || out_features <= 0 || in_features <= 0 || in_features % 256 != 0 || tgo_block_bytes(quant_type) < 0) return 0;
+    int cg = wanted_cta_group();
+    int pairs = 0;
+    if (cg == 2) {
+        pairs = max_pairs(quant_type, kBwd);
+        if (pairs < 1) cg = 1;
+    }
+    int split_steps = 0;
+    const int n = plan_split(rows, out_features, in_features, static_cast<int64_t>(kTileM) * cg, cg == 2 ? pairs : num_sms(), split_steps);
+    return n > 1 ? static_cast<int64_t>(n) * rows * in_features * 4 : 0;
+}
+
+int tgo_mmq_dx_ws(const void* dy, const void* packed_weight, void* dx, int64_t rows, int64_t out_features,
+                  int64_t in_features, int quant_type, void* workspace, int64_t workspace_bytes, void* stream) {
+    Problem p = {};
+    p.act[0] = dy; p.wgt[0] = packed_weight; p.out[0] = dx; p.nsets = 1;
+    p.rows = rows; p.N = out_features; p.K = in_features; p.E = 1; p.qt = quant_type; p.mode = kBwd;
+    p.ws = workspace; p.ws_bytes = workspace_bytes;
     return run_problem(p, static_cast<cudaStream_t>(stream));
 }
 

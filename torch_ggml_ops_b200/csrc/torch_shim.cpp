@@ -130,6 +130,17 @@ Tensor mmq_grad_input_op(const Tensor& grad_output, const Tensor& packed_weight,
     std::vector<int64_t> sizes(grad_output.sizes().begin(), grad_output.sizes().end());
     sizes.back() = in_features;
     Tensor grad_input = new_bf16(grad_output, sizes);
+    // few rows against very many out-features (an LM head): the reduction is split over the CTA
+    // pairs and its fp32 partial sums need a per-call workspace, a fresh tensor like the outputs
+    const int64_t ws_bytes = tgo_mmq_dx_workspace_bytes(s.rows, s.red, in_features, static_cast<int>(quant_type));
+    if (ws_bytes > 0) {
+        Tensor workspace = new_bytes(grad_output, ws_bytes);
+        check_call(tgo_mmq_dx_ws(grad_output.const_data_ptr(), packed_weight.const_data_ptr(), grad_input.mutable_data_ptr(),
+                                 s.rows, s.red, in_features, static_cast<int>(quant_type), workspace.mutable_data_ptr(),
+                                 ws_bytes, current_stream(device)),
+                   "mmq_grad_input");
+        return grad_input;
+    }
     check_call(tgo_mmq_dx(grad_output.const_data_ptr(), packed_weight.const_data_ptr(), grad_input.mutable_data_ptr(),
                           s.rows, s.red, in_features, static_cast<int>(quant_type), current_stream(device)),
                "mmq_grad_input");

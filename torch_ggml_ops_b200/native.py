@@ -25,6 +25,8 @@ SIGNATURES = {
     "tgo_dequantize_bf16": (_i32, [_vp, _i64, _i32, _vp, _vp]),
     "tgo_mmq_fwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "tgo_mmq_dx": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "tgo_mmq_dx_workspace_bytes": (_i64, [_i64, _i64, _i64, _i32]),
+    "tgo_mmq_dx_ws": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
     "tgo_mmq_fwd_multi": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tgo_grouped_workspace_bytes": (_i64, [_i64, _i64]),
     "tgo_build_tiles": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
@@ -122,6 +124,18 @@ def mmq_fwd(x, packed, y, rows, out_features, in_features, quant_type, stream=No
 def mmq_dx(dy, packed, dx, rows, out_features, in_features, quant_type, stream=None) -> None:
     check(lib().tgo_mmq_dx(_ptr(dy), _ptr(packed), _ptr(dx), rows, out_features, in_features, quant_type,
                            _stream(stream)), "tgo_mmq_dx")
+
+
+def mmq_dx_split(dy, packed, dx, rows, out_features, in_features, quant_type, stream=None) -> int:
+    """Input gradient with the split reduction where it applies (``tgo_mmq_dx_ws``); allocates the
+    workspace with torch.  Returns the workspace bytes used (0: same launch as ``mmq_dx``)."""
+    import torch
+
+    need = int(lib().tgo_mmq_dx_workspace_bytes(rows, out_features, in_features, quant_type))
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dy.device)
+    check(lib().tgo_mmq_dx_ws(_ptr(dy), _ptr(packed), _ptr(dx), rows, out_features, in_features, quant_type,
+                              _ptr(ws) if need else None, need, _stream(stream)), "tgo_mmq_dx_ws")
+    return need
 
 
 def mmq_fwd_multi(x, packed_list, y_list, rows, out_features, in_features, quant_type, stream=None) -> None:
