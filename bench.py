@@ -359,7 +359,8 @@ def gpu_arm(args):
     # routing sort, dispatch to the owning GPU, grouped matmuls, return.  Receive buffers hold twice
     # the mean load when experts are spread over several GPUs (the routing is skewed).
     cap = R if world == 1 else 2 * R
-    pep = PeerExpertParallel(w, qt, E, N, K, capacity_rows=cap, tokens_per_rank=T if args.token_level else None, top_k=top_k)
+    pep = PeerExpertParallel(w, qt, E, N, K, capacity_rows=cap, tokens_per_rank=T if args.token_level else None, top_k=top_k,
+                             fences=args.fences)
     y_out = [torch.empty(R, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]
     dx_out = [torch.empty(T, K, dtype=torch.bfloat16, device=dev) for _ in range(2)]
 
@@ -446,9 +447,9 @@ def gpu_arm(args):
         clocks = sampler.stop()
         # this library's kernels per step: GEMMs + tile builders (4), routing sort (3), plan (2, + 1 for the
         # token maps), exchange (pair level 4; token level 6: dispatch, expand, pull y, dispatch dy, reduce, pull)
-        launches = 4 + 3 + (3 + 6 if args.token_level else 2 + 4)
-        executor = (f"{world} GPUs: experts sharded; dispatch/combine by peer-memory kernels over NVLink, NCCL only for "
-                    "counts and fences")
+        launches = 4 + 3 + (3 + 6 if args.token_level else 2 + 4) + (6 if args.fences == "peer" else 0)   # + count exchange, 5 barriers
+        executor = (f"{world} GPUs: experts sharded; dispatch/combine by peer-memory kernels over NVLink (NCCL only for "
+                    "the host-side setup; counts and phase barriers by peer memory too unless --fences nccl)")
     result["device_status"] = native.device_status()
     result["ep_overflow"] = int(pep.overflow.item())
 
@@ -573,7 +574,8 @@ def config5_step(args, world, rank, dev, seed, PeerMoEMLP, native, barrier, max_
     dy = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
     rows = T * top_k
     cap = rows if world == 1 else rows + rows // 2
-    mlp = PeerMoEMLP(wg, wu, wd, c5["qt_gate_up"], c5["qt_down"], E, H, F, capacity_rows=cap, tokens_per_rank=T, top_k=top_k)
+    mlp = PeerMoEMLP(wg, wu, wd, c5["qt_gate_up"], c5["qt_down"], E, H, F, capacity_rows=cap, tokens_per_rank=T, top_k=top_k,
+                     fences=args.fences)
     y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
     dx = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
 
@@ -716,6 +718,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--parity-tokens", type=int, default=32, help="tokens per rank checked against the oracle (not timed)")
     ap.add_argument("--parity-tokens-mlp", type=int, default=6, help="tokens per rank checked in the MoE feed-forward step")
+    ap.add_argument("--fences", choices=["peer", "nccl"], default="peer",
+                    help="multi-GPU: order the ranks' phases by this library's peer-memory barrier kernel or by NCCL collectives")
     ap.add_argument("--no-config5", action="store_true", help="skip the expert-parallel MoE feed-forward configuration")
     ap.add_argument("--pair-level", dest="token_level", action="store_false",
                     help="multi-GPU peer exchange: move one row per routed pair instead of one per (token, destination GPU)")

@@ -194,6 +194,22 @@ int tgo_quantize_q8(const void* x, int64_t rows, int64_t width, void* q, float* 
  * the host layer orders the phases with stream-ordered collectives (dispatch | barrier | grouped
  * matmul | barrier | pull). */
 
+/* Stream-ordered barrier between the ranks by peer memory alone (no collective library): rank r
+ * stores `epoch` (which must grow by one with every barrier of a series) into slot r of every rank's
+ * flag array (flag_ptrs[g] = rank g's int32[world] array, zero-initialised, peer-addressable) and
+ * waits until all slots of its own array have reached `epoch`.  Everything this GPU wrote to peer
+ * memory before the call is visible to a peer's kernels launched after that peer's call returns.
+ * The wait is bounded by limit_cycles SM cycles (1000..4000000000); when it runs out, code 11 is
+ * recorded in the status word (tgo_device_status) and the kernel returns. */
+int tgo_ep_barrier(void* const* flag_ptrs, int64_t world, int64_t my_rank, int64_t epoch,
+                   int64_t limit_cycles, void* stream);
+
+/* counts_all[g][my_rank][:] = counts[:] for every rank g: the all-gather of the per-expert pair
+ * counts (tgo_route_sort's expert_counts) by peer stores; table_ptrs[g] = rank g's
+ * int32[world][num_experts] table.  Follow with tgo_ep_barrier before reading the table. */
+int tgo_ep_share_counts(const int32_t* counts, int64_t num_experts, int64_t my_rank,
+                        void* const* table_ptrs, int64_t world, void* stream);
+
 /* From the per-expert pair counts of all ranks (counts_all int32[world][num_experts], identical
  * on every rank) and this rank's routing (expert_ids, pair_to_sorted from tgo_route_sort):
  * dst_rank / dst_row int32[n_pairs] = where each routed pair goes (-1 if dropped; *overflow is set

@@ -169,3 +169,36 @@ def test_overflow_is_surfaced_by_the_wrapper(cuda):
     pep2_ids = to_dev(torch.from_numpy(ids[:20].copy()))
     pep.plan(pep2_ids)
     pep.check_overflow()
+
+
+def test_rank_barrier_and_count_exchange_kernels(cuda):
+    """The peer-memory rank barrier on one GPU: with every flag already set it passes at once; with
+    a peer that never arrives its bounded wait runs out, the status word records code 11 and the
+    context stays usable (no kernel ever waits on another launch here: rank 1 simply never calls)."""
+    from torch_ggml_ops_b200 import native
+
+    world, E = 2, 8
+    flags = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    tables = [torch.full((world, E), -1, dtype=torch.int32, device="cuda") for _ in range(world)]
+    ptrs = lambda bufs: [b.data_ptr() for b in bufs]  # noqa: E731
+    for r in range(world):
+        native.ep_share_counts(torch.arange(E, dtype=torch.int32, device="cuda") + 10 * r, r, ptrs(tables))
+    torch.cuda.synchronize()
+    for t in tables:
+        assert t.cpu().tolist() == [list(range(E)), list(range(10, 10 + E))]
+    # rank 1 "arrived" already (its slot holds the epoch everywhere): rank 0 passes
+    for f in flags:
+        f[1] = 1
+    assert native.device_status() == 0
+    native.ep_barrier(ptrs(flags), 0, 1, limit_cycles=2_000_000)
+    torch.cuda.synchronize()
+    assert native.device_status() == 0
+    assert flags[0].cpu().tolist()[:2] == [1, 1] and flags[1].cpu().tolist()[:2] == [1, 1]
+    # epoch 2: rank 1 never signals; the wait gives up after about a millisecond
+    native.ep_barrier(ptrs(flags), 0, 2, limit_cycles=2_000_000)
+    torch.cuda.synchronize()
+    status = native.device_status()
+    assert status & 0xFF == 11 and status >> 8 == 1          # code, and the rank that was missing
+    assert native.device_status() == 0
+    x = torch.ones(8, device="cuda") * 2                      # the context still works
+    assert float(x.sum()) == 16.0

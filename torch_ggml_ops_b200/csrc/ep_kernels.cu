@@ -270,6 +270,46 @@ __global__ void __launch_bounds__(256) ep_pull_tokens_kernel(const __grid_consta
     }
 }
 
+// ---------------------------------------------------------------- rank barrier and count exchange
+// Stream-ordered barrier between the ranks without a collective library: rank r stores `epoch`
+// into slot r of every rank's flag array (system-scope release, after a system fence that makes
+// this GPU's earlier peer stores visible), then waits until every slot of its own array has reached
+// `epoch`.  The wait is bounded: after `limit_cycles` it records kAbortRankBarrier in the status
+// word and returns, so a missing peer costs a wrong step, not a hung GPU.  One block of 64 threads.
+constexpr int kAbortRankBarrier = 11;
+
+__global__ void __launch_bounds__(64) ep_barrier_kernel(const __grid_constant__ PeerPtrs flags, int world, int me, int epoch,
+                                                        long long limit_cycles, int* __restrict__ status) {
+    const int r = threadIdx.x;
+    __threadfence_system();
+    if (r < world) {
+        int* slot = static_cast<int*>(flags.p[r]) + me;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(slot), "r"(epoch) : "memory");
+        const int* mine = static_cast<const int*>(flags.p[me]) + r;
+        const long long t0 = clock64();
+        bool ok = false;
+        for (unsigned polls = 0;; ++polls) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (v - epoch >= 0) { ok = true; break; }          // epochs only grow (wrap-safe comparison)
+            if ((polls & 63u) == 63u && clock64() - t0 > limit_cycles) break;
+        }
+        if (!ok && status != nullptr) atomicCAS(status, 0, kAbortRankBarrier | (r << 8));
+    }
+    __syncthreads();
+    __threadfence_system();
+}
+
+// counts_all[g][me][:] = counts[:] on every rank g (the all-gather of the per-expert pair counts,
+// by plain peer stores; a rank barrier must follow before anybody reads its table).
+__global__ void __launch_bounds__(256) ep_share_counts_kernel(const int32_t* __restrict__ counts, int E, int me, int world,
+                                                              const __grid_constant__ PeerPtrs tables) {
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < E * world; i += 256 * gridDim.x) {
+        const int g = i / E, e = i - g * E;
+        static_cast<int32_t*>(tables.p[g])[static_cast<long long>(me) * E + e] = counts[e];
+    }
+}
+
 static int ep_grid(long long work_items) {
     long long blocks = (work_items + 255) / 256;
     if (blocks > 148LL * 8) blocks = 148LL * 8;
@@ -316,6 +356,35 @@ int tgo_ep_plan(const int32_t* counts_all, int64_t world, int64_t num_experts, i
         expert_ids, pair_to_sorted, scratch, scratch + E, static_cast<int>(n_pairs), E, EL, static_cast<int>(capacity),
         dst_rank, dst_row, overflow);
     return ep_launch_check("expert-parallel plan kernel launch failed");
+}
+
+int* tgo_status_word(void);   // tgo_api.cu
+
+int tgo_ep_barrier(void* const* flag_ptrs, int64_t world, int64_t my_rank, int64_t epoch, int64_t limit_cycles, void* stream) {
+    if (world <= 0 || world > kEpMaxRanks || my_rank < 0 || my_rank >= world)
+        return route_fail(TGO_E_ARG, "world size must be in 1..64 and the rank inside it");
+    if (limit_cycles < 1000 || limit_cycles > 4000000000LL)
+        return route_fail(TGO_E_ARG, "limit_cycles must be in 1000..4000000000 (about two seconds)");
+    PeerPtrs pp = {};
+    const int rc = fill_peers(pp, flag_ptrs, world);
+    if (rc != TGO_OK) return rc;
+    ep_barrier_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(pp, static_cast<int>(world), static_cast<int>(my_rank),
+                                                                        static_cast<int>(epoch), limit_cycles, tgo_status_word());
+    return ep_launch_check("ep_barrier_kernel launch failed");
+}
+
+int tgo_ep_share_counts(const int32_t* counts, int64_t num_experts, int64_t my_rank, void* const* table_ptrs, int64_t world,
+                        void* stream) {
+    if (counts == nullptr) return route_fail(TGO_E_ARG, "null pointer");
+    if (num_experts <= 0 || num_experts > 4096 || world <= 0 || world > kEpMaxRanks || my_rank < 0 || my_rank >= world)
+        return route_fail(TGO_E_ARG, "num_experts must be in 1..4096, the world size in 1..64 and the rank inside it");
+    PeerPtrs pp = {};
+    const int rc = fill_peers(pp, table_ptrs, world);
+    if (rc != TGO_OK) return rc;
+    const int n = static_cast<int>(num_experts * world);
+    ep_share_counts_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        counts, static_cast<int>(num_experts), static_cast<int>(my_rank), static_cast<int>(world), pp);
+    return ep_launch_check("ep_share_counts_kernel launch failed");
 }
 
 int tgo_ep_dispatch(const void* src, int64_t divisor, const int32_t* dst_rank, const int32_t* dst_row, int64_t n_pairs,

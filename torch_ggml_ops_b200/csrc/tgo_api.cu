@@ -75,6 +75,11 @@ static const uint64_t* grid_ptr() {
     return p;
 }
 
+}  // namespace tgo
+// the status word for the other translation units of the library (null if the lookup fails)
+extern "C" int* tgo_status_word(void) { return tgo::status_ptr(); }
+namespace tgo {
+
 // ------------------------------------------------------------------ tensor maps
 static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;

@@ -30,7 +30,7 @@ import torch.distributed as dist
 
 from . import native
 
-PEER_BUFFERS = ("tok_in", "y_part", "dy_in", "dx_part", "row_slot", "slot_rows", "row_weight")
+PEER_BUFFERS = ("tok_in", "y_part", "dy_in", "dx_part", "row_slot", "slot_rows", "row_weight", "flags", "counts_tab")
 
 
 class MoEMLPRank:
@@ -60,11 +60,13 @@ class MoEMLPRank:
         shapes = {"tok_in": (self.slots, self.H, bf), "y_part": (self.slots, self.H, bf),
                   "dy_in": (self.slots, self.H, bf), "dx_part": (self.slots, self.H, bf),
                   "row_slot": (self.cap, 1, i32), "slot_rows": (self.slots, self.top_k, i32),
-                  "row_weight": (self.cap, 1, torch.float32)}
+                  "row_weight": (self.cap, 1, torch.float32),
+                  "flags": (1, max(self.world, 2), i32), "counts_tab": (self.world, self.E, i32)}
         self.buf = {name: alloc(name, *shapes[name]) for name in PEER_BUFFERS}
         self.buf["slot_rows"].fill_(-1)   # a slot nobody has announced names no row
         self.buf["row_slot"].fill_(-1)    # a row nobody has announced names no slot
         self.buf["row_weight"].fill_(1.0)
+        self.buf["flags"].zero_()         # rank barrier epochs start from zero
         # expert-major rows of this rank only; the wide buffers serve forward and backward in turn
         self.rows_a = torch.empty(self.cap, self.H, dtype=bf, device=dev)   # x rows, then dy rows
         self.rows_b = torch.empty(self.cap, self.H, dtype=bf, device=dev)   # y rows, then dx rows
@@ -175,7 +177,13 @@ class PeerMoEMLP:
     initialised for more than one rank).  ``step`` order: ``plan`` -> ``forward`` -> ``grad_input``."""
 
     def __init__(self, w_gate, w_up, w_down, qt_gate_up, qt_down, num_experts, hidden, ffn, capacity_rows,
-                 tokens_per_rank, top_k, group=None):
+                 tokens_per_rank, top_k, group=None, fences: str = "peer"):
+        """``fences``: "peer" orders the ranks' phases with this library's barrier kernel over peer
+        memory (bounded wait; no collective library inside a step), "nccl" with one-element
+        all-reduces and an all-gather of the counts."""
+        if fences not in ("peer", "nccl"):
+            raise ValueError("fences must be 'peer' or 'nccl'")
+        self.fences, self._epoch = fences, 0
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -201,17 +209,27 @@ class PeerMoEMLP:
         self._token = torch.zeros(1, dtype=torch.int32, device=dev)
         self._counts_all = torch.empty(self.world, num_experts, dtype=torch.int32, device=dev)
         if self.world > 1:
+            torch.cuda.synchronize()
             dist.barrier(group=group)   # everybody has filled its maps before anybody writes into them
 
     def _fence(self) -> None:
         """All ranks have finished everything they enqueued before this point (stream-ordered)."""
-        if self.world > 1:
+        if self.world == 1:
+            return
+        if self.fences == "peer":
+            self._epoch += 1
+            native.ep_barrier(self.r.peers["flags"], self.r.rank, self._epoch)
+        else:
             dist.all_reduce(self._token, group=self.group)
 
     def plan(self, topk_ids: torch.Tensor, weights: torch.Tensor | None = None) -> None:
         counts = self.r.route(topk_ids)
-        if self.world > 1:
-            # also orders the ranks: the peers' previous step is over before their maps are rewritten
+        # either form also orders the ranks: the peers' previous step is over before their maps are rewritten
+        if self.world > 1 and self.fences == "peer":
+            native.ep_share_counts(counts, self.r.rank, self.r.peers["counts_tab"])
+            self._fence()
+            counts_all = self.r.buf["counts_tab"]
+        elif self.world > 1:
             dist.all_gather_into_tensor(self._counts_all, counts, group=self.group)
             counts_all = self._counts_all
         else:

@@ -38,6 +38,8 @@ SIGNATURES = {
     "tgo_combine_rows": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tgo_quantize_q8": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     "tgo_ep_plan": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "tgo_ep_barrier": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp]),
+    "tgo_ep_share_counts": (_i32, [_vp, _i64, _i64, _vp, _i64, _vp]),
     "tgo_ep_dispatch": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _vp, _i64, _vp]),
     "tgo_ep_pull": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tgo_ep_token_maps": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _vp]),
@@ -256,6 +258,18 @@ def ep_plan(counts_all, my_rank, expert_ids, pair_to_sorted, capacity, stream=No
                             _ptr(dst_rank), _ptr(dst_row), _ptr(li), _ptr(lo), _ptr(scratch), _ptr(overflow),
                             _stream(stream)), "tgo_ep_plan")
     return dst_rank, dst_row, li, lo, overflow
+
+
+def ep_barrier(flag_ptrs, my_rank, epoch, limit_cycles=2_000_000_000, stream=None) -> None:
+    """Stream-ordered rank barrier over peer memory with a bounded wait (``tgo_ep_barrier``)."""
+    check(lib().tgo_ep_barrier(_ptr_array(flag_ptrs), len(flag_ptrs), my_rank, epoch, limit_cycles, _stream(stream)),
+          "tgo_ep_barrier")
+
+
+def ep_share_counts(counts, my_rank, table_ptrs, stream=None) -> None:
+    """Writes this rank's per-expert pair counts into every rank's table (``tgo_ep_share_counts``)."""
+    check(lib().tgo_ep_share_counts(_ptr(counts), counts.numel(), my_rank, _ptr_array(table_ptrs), len(table_ptrs),
+                                    _stream(stream)), "tgo_ep_share_counts")
 
 
 def ep_dispatch(src, divisor, dst_rank, dst_row, peer_ptrs, stream=None) -> None:

@@ -43,7 +43,14 @@ class PeerExpertParallel:
 
     def __init__(self, local_weight: torch.Tensor, quant_type: int, num_experts: int, out_features: int,
                  in_features: int, capacity_rows: int, group=None, tokens_per_rank: int | None = None,
-                 top_k: int | None = None):
+                 top_k: int | None = None, fences: str = "peer"):
+        """``fences``: how the ranks' phases are ordered - "peer": this library's barrier kernel over
+        peer memory (bounded wait, no collective library in the step); "nccl": one-element all-reduces
+        and an all-gather of the counts."""
+        if fences not in ("peer", "nccl"):
+            raise ValueError("fences must be 'peer' or 'nccl'")
+        self.fences = fences
+        self._epoch = 0
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -60,6 +67,7 @@ class PeerExpertParallel:
         shapes = {"x_in": (self.cap, self.K, torch.bfloat16), "y_out": (self.cap, self.N, torch.bfloat16),
                   "dy_in": (self.cap, self.N, torch.bfloat16), "dx_out": (self.cap, self.K, torch.bfloat16)}
         self.token_level = tokens_per_rank is not None and top_k is not None
+        shapes.update({"flags": (1, max(self.world, 2), torch.int32), "counts_tab": (self.world, self.E, torch.int32)})
         if self.token_level:
             self.tpr, self.top_k = int(tokens_per_rank), int(top_k)
             slots = self.world * self.tpr
@@ -81,14 +89,17 @@ class PeerExpertParallel:
                 t = torch.empty(rows, cols, dtype=dtype, device=dev)
                 self.buf[name] = t
                 self.peers[name] = [t.data_ptr()]
+        self.buf["flags"].zero_()
         if self.token_level:
             # a slot nobody has written yet must not name a row, and a row nobody has announced must
-            # not name a slot outside the token buffer; peers write into these buffers from their
-            # first plan on, so everybody finishes the fills before anybody goes on
+            # not name a slot outside the token buffer
             self.buf["slot_rows"].fill_(-1)
             self.buf["row_slot"].fill_(-1)
-            if self.world > 1:
-                dist.barrier(group=group)
+        if self.world > 1:
+            # peers write into these buffers from their first plan on, so everybody finishes the
+            # fills before anybody goes on
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
         self.ws = torch.empty(native.grouped_workspace_bytes(self.cap, self.EL), dtype=torch.uint8, device=dev)
         self._token = torch.zeros(1, dtype=torch.int32, device=dev)
         self.overflow = None
@@ -97,7 +108,12 @@ class PeerExpertParallel:
     # ------------------------------------------------------------------ ordering between ranks
     def _fence(self) -> None:
         """All ranks have finished everything they enqueued before this point (stream-ordered)."""
-        if self.world > 1:
+        if self.world == 1:
+            return
+        if self.fences == "peer":
+            self._epoch += 1
+            native.ep_barrier(self.peers["flags"], self.rank, self._epoch)
+        else:
             dist.all_reduce(self._token, group=self.group)
 
     # ------------------------------------------------------------------ routing
@@ -130,7 +146,13 @@ class PeerExpertParallel:
         b = self._plan_bufs
         b["overflow"].zero_()   # the flag describes this plan only
         _, p2s, _, _ = native.route_sort(flat, self.E, out=b)
-        if self.world > 1:
+        if self.world > 1 and self.fences == "peer":
+            # every rank writes its counts into every rank's table; the barrier also tells this rank
+            # that the peers' previous step is over before their maps are rewritten below
+            native.ep_share_counts(b["counts"], self.rank, self.peers["counts_tab"])
+            self._fence()
+            counts_all = self.buf["counts_tab"]
+        elif self.world > 1:
             counts_all = b["counts_all"]
             dist.all_gather_into_tensor(counts_all, b["counts"], group=self.group)
         else:
