@@ -9,8 +9,9 @@ back (forward: the weighted sum of the token's down-projection rows on that GPU;
 of its input-gradient rows).  The routing weight of a pair travels with the plan to the pair's
 owner and is applied inside the activation kernels, so nothing per routed pair ever crosses NVLink.
 Rows move by this library's peer-memory kernels (plain 16-byte peer stores and loads, no multicast,
-no wait inside any kernel); the phases of different ranks are ordered by stream-ordered one-element
-all-reduces.
+no wait inside any of those kernels); the phases of different ranks are ordered by a one-block
+barrier kernel over peer memory whose wait is bounded (``tgo_ep_barrier``), or by one-element
+all-reduces (``fences="nccl"``).
 
 The reference has no such block: it stops at the matmul pair and leaves activation, down
 projection and combine to its caller (README.md:3, csrc/mmq_hip.cu:1054-1193); each rank's buffers
@@ -19,7 +20,7 @@ int32 cumulative end offsets: csrc/mmq_hip.cu:325-406).
 
 ``MoEMLPRank`` holds one rank's state and runs one phase at a time without any collective, so a
 test can step several virtual ranks on one GPU in lockstep; ``PeerMoEMLP`` is the real thing, one
-per process, with the collectives between the phases.
+per process, with the barriers between the phases.
 """
 from __future__ import annotations
 

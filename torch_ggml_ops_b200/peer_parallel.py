@@ -19,8 +19,9 @@ move one row per (token, destination GPU) instead of one per routed pair - a tok
 to every GPU that owns one of its experts and is replicated into the expert-major buffer there
 (tgo_ep_dispatch_tokens + tgo_ep_expand), and the input gradient comes back as one partial sum per
 GPU (tgo_ep_reduce + tgo_ep_pull_tokens).  With 8 experts per token this cuts the NVLink bytes of
-those exchanges by 4x on 2 GPUs and 2.2x on 4.  "fence" is a stream-ordered one-element all-reduce: it orders the ranks'
-phases without any spin-wait in our kernels.  Multicast is never used (the symmetric-memory
+those exchanges by 4x on 2 GPUs and 2.2x on 4.  "fence" orders the ranks' phases: by default a one-block
+barrier kernel over peer memory with a bounded wait (tgo_ep_barrier), optionally a stream-ordered
+one-element all-reduce (fences="nccl"); the exchange kernels themselves never wait.  Multicast is never used (the symmetric-memory
 allocator is told not to bind a multicast object).
 
 The reference has no multi-GPU path; the per-rank contract it defines (rows sorted by expert +
