@@ -211,7 +211,7 @@ __device__ __forceinline__ int half_tokens(const TileInfo& t, int half) { return
 __device__ __forceinline__ int half_row0(const TileInfo& t, int half) { return half == 0 ? t.row0 : t.row0 + t.tok0; }
 
 // `mtiles` / `mtiles_set` count tiles of CG * 128 weight rows; `rank` is the CTA's rank in its pair.
-template <int MODE, int CG, int WIDE>
+template <int MODE, int CG, int WIDE, int SPLIT>
 __device__ __forceinline__ bool load_tile(const GemmArgs& a, int tile, int mtiles, int mtiles_set,
                                           int rank, TileInfo& t) {
     const int task = tile / mtiles;
@@ -239,7 +239,7 @@ __device__ __forceinline__ bool load_tile(const GemmArgs& a, int tile, int mtile
         t.m0 = ((mt - t.set * mtiles_set) * CG + rank) * kTileM;
     } else {
         t.set = 0;
-        t.split = mt / mtiles_set;                      // 0 unless the reduction is split
+        t.split = SPLIT ? mt / mtiles_set : 0;          // which range of a split reduction
         t.m0 = ((mt - t.split * mtiles_set) * CG + rank) * kTileM;
     }
     return t.ntok > 0;
@@ -263,8 +263,10 @@ __device__ __forceinline__ bool all_wait(uint32_t bar, uint32_t parity, volatile
 }
 
 // WIDE = 0: every tile has at most 256 tokens and one accumulator (the wide-tile paths compile
-// out); WIDE = 1: tiles of up to 512 tokens.
-template <int QT, int MODE, int CG, int WIDE>
+// out); WIDE = 1: tiles of up to 512 tokens.  SPLIT = 1 (backward, narrow tiles only): the
+// reduction is cut into ranges with fp32 partial sums; compiled out otherwise (measured: carrying
+// the split arithmetic in the ordinary backward kernel cost it 4 %).
+template <int QT, int MODE, int CG, int WIDE, int SPLIT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     using Cfg = GemmCfg<QT, MODE, CG, WIDE>;
@@ -312,7 +314,8 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     const int nkb = K >> 8;
     // tile space
     const int mtiles_set = MODE == kFwd ? (N + CG * kTileM - 1) / (CG * kTileM) : K / (CG * kTileM);
-    const int nsplit = MODE == kBwd ? args.nsplit : 1;
+    static_assert(!SPLIT || (MODE == kBwd && !WIDE), "the split reduction exists for the narrow backward kernel only");
+    const int nsplit = SPLIT ? args.nsplit : 1;
     const int mtiles = MODE == kFwd ? mtiles_set * args.nsets : mtiles_set * nsplit;
     const int steps_set = MODE == kFwd ? K / kStepK : (N + kStepK - 1) / kStepK;
     // 64-element steps of a tile: the whole reduction (both weight sets of a pair backward), or one
@@ -372,7 +375,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 bool ok = true;
                 for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                     TileInfo t;
-                    if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+                    if (!load_tile<MODE, CG, WIDE, SPLIT>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                     const int npipe = nstages * t.nhalf;
                     for (int ps = 0; ps < npipe; ++ps, ++it) {
                         const int stage = t.nhalf == 2 ? ps >> 1 : ps;
@@ -393,7 +396,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
 #pragma unroll
                         for (int ks = 0; ks < KS; ++ks) {
                             const int step = stage * KS + ks;
-                            const int astep = MODE == kFwd ? step : t.split * nsteps + step;   // step of the whole reduction
+                            const int astep = SPLIT ? t.split * nsteps + step : step;   // step of the whole reduction
                             int set = MODE == kFwd ? 0 : astep / steps_set;
                             // a step past the end reads columns outside the matrix: TMA fills zeros
                             int red0 = (MODE == kFwd ? step : astep - set * steps_set) * kStepK;
@@ -424,7 +427,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             const int red_total = MODE == kFwd ? K : N;
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+                if (!load_tile<MODE, CG, WIDE, SPLIT>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 const int npipe = nstages * t.nhalf;
                 for (int ps = 0; ps < npipe; ++ps, ++it) {
                     const int stage = t.nhalf == 2 ? ps >> 1 : ps;
@@ -439,7 +442,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     }
                     for (int ks = 0; ks < KS; ++ks) {
                         const int step = stage * KS + ks;
-                        const int astep = MODE == kFwd ? step : t.split * nsteps + step;
+                        const int astep = SPLIT ? t.split * nsteps + step : step;
                         int set = MODE == kFwd ? 0 : astep / steps_set;
                         int red0 = (MODE == kFwd ? step : astep - set * steps_set) * kStepK;
                         if (step >= nsteps || astep >= steps_all) { set = 0; red0 = red_total; }   // a step past the end: zeros
@@ -492,7 +495,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             bool ok = true, ready = false;
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+                if (!load_tile<MODE, CG, WIDE, SPLIT>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 const uint32_t acc0 = tl & 1u, acc1 = acc0 ^ 1u;
                 if (!mbar_wait(bar_acc_empty + 8 * acc0, ((tl >> 1) & 1u) ^ 1u, abort_word, kAbortAccEmpty)) break;
                 tc_fence_after_sync();
@@ -574,7 +577,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 for (int c = 0; c < P; ++c) prefetch_tmap(&args.wgt_maps[s].cls[c]);
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
-                if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+                if (!load_tile<MODE, CG, WIDE, SPLIT>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 const int nraw = MODE == kFwd ? nkb : nsteps_pad;
                 for (int ri = 0; ri < nraw; ++ri, ++itr) {
                     const uint32_t r = itr % NR, ph = (itr / NR) & 1u;
@@ -583,7 +586,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     if (MODE == kFwd) {
                         set = t.set; n_first = t.m0; kb = ri;
                     } else {
-                        const int astep = t.split * nsteps + ri;
+                        const int astep = SPLIT ? t.split * nsteps + ri : ri;
                         set = astep / steps_set; n_first = (astep - set * steps_set) * kStepK; kb = t.m0 >> 8;
                         if (ri >= nsteps || astep >= steps_all) { set = 0; n_first = 0; }   // a step past the end: decoded as zeros
                     }
@@ -708,7 +711,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
 
         for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
             TileInfo t;
-            if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+            if (!load_tile<MODE, CG, WIDE, SPLIT>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
             wide = t.nhalf == 2;
             if (WIDE) {
                 // this group's first step of the tile (running index parity equals the group)
@@ -755,7 +758,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     const uint32_t ri = d0 + step;
                     const uint32_t r = ri % NR, rph = (ri / NR) & 1u;
                     if (!all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull)) { ok = false; break; }
-                    const int astep = t.split * nsteps + step;
+                    const int astep = SPLIT ? t.split * nsteps + step : step;
                     const int n_first = (astep >= steps_set ? astep - steps_set : astep) * kStepK;
                     const bool valid = step < nsteps && astep < steps_all && n_first + row < N;
                     if (!emit(blk0 + r * Cfg::kRawStageBytes, g, valid, bar_raw_empty + 8 * r)) { ok = false; break; }
@@ -781,7 +784,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             const uint32_t taddr = tmem_base + acc * kTileTok + (static_cast<uint32_t>(quad * 32) << 16);
             const int mq = m0 + quad * 32;  // first output column of this warp
             __nv_bfloat16* out_base = args.out[MODE == kFwd ? set : 0] + static_cast<long long>(row0) * mdim;
-            if (MODE == kBwd && args.partial != nullptr) {
+            if (SPLIT && args.partial != nullptr) {
                 // split reduction: fp32 partial sums, lane = output column (128 bytes per warp store)
                 const int m = mq + lane;
                 float* part = args.partial + (static_cast<long long>(split) * args.rows + row0) * mdim + m;
@@ -844,7 +847,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         uint32_t tl = 0;
         for (long long tile = cta; tile < total_tiles; tile += ncta) {
             TileInfo t;
-            if (!load_tile<MODE, CG, WIDE>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+            if (!load_tile<MODE, CG, WIDE, SPLIT>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
             if (!drain(tl, t.m0, t.set, t.row0, t.tok0, t.split)) break;
             ++tl;
             if (WIDE && t.nhalf == 2) {   // the second half of a wide tile is an accumulator of its own

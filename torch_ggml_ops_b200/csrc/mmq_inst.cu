@@ -11,7 +11,7 @@
 
 namespace tgo {
 
-template <int QT, int MODE, int CG, int WIDE>
+template <int QT, int MODE, int CG, int WIDE, int SPLIT>
 static cudaError_t configure() {
     using Cfg = GemmCfg<QT, MODE, CG, WIDE>;
     // relaxed atomics: threads that race on a device's first call set the same attribute and flag
@@ -20,14 +20,14 @@ static cudaError_t configure() {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 64 && configured[dev].load(std::memory_order_relaxed)) return cudaSuccess;
-    e = cudaFuncSetAttribute(mmq_gemm_kernel<QT, MODE, CG, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(mmq_gemm_kernel<QT, MODE, CG, WIDE, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     if (dev < 64) configured[dev].store(true, std::memory_order_relaxed);
     return cudaSuccess;
 }
 
-template <int QT, int MODE, int CG, int WIDE>
+template <int QT, int MODE, int CG, int WIDE, int SPLIT>
 static void fill_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute& attr, int grid, cudaStream_t stream) {
     using Cfg = GemmCfg<QT, MODE, CG, WIDE>;
     cfg = cudaLaunchConfig_t{};
@@ -43,23 +43,25 @@ static void fill_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute& attr, int 
     cfg.numAttrs = 1;
 }
 
-template <int QT, int MODE, int CG, int WIDE>
+template <int QT, int MODE, int CG, int WIDE, int SPLIT>
 static int launch_one(const GemmArgs& args, int grid, cudaStream_t stream) {
-    cudaError_t e = configure<QT, MODE, CG, WIDE>();
+    cudaError_t e = configure<QT, MODE, CG, WIDE, SPLIT>();
     if (e != cudaSuccess) return static_cast<int>(e);
     if (CG == 1) {
-        mmq_gemm_kernel<QT, MODE, CG, WIDE><<<grid, kGemmThreads, GemmCfg<QT, MODE, CG, WIDE>::kSmemBytes, stream>>>(args);
+        mmq_gemm_kernel<QT, MODE, CG, WIDE, SPLIT><<<grid, kGemmThreads, GemmCfg<QT, MODE, CG, WIDE>::kSmemBytes, stream>>>(args);
         return static_cast<int>(cudaGetLastError());
     }
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr;
-    fill_config<QT, MODE, CG, WIDE>(cfg, attr, grid, stream);
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, mmq_gemm_kernel<QT, MODE, CG, WIDE>, args));
+    fill_config<QT, MODE, CG, WIDE, SPLIT>(cfg, attr, grid, stream);
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, mmq_gemm_kernel<QT, MODE, CG, WIDE, SPLIT>, args));
 }
 
+// the kernel variant for this launch: wide tiles, or (backward only) a split reduction, or neither
 template <int QT, int MODE, int CG>
 static int launch_width(int wide, const GemmArgs& args, int grid, cudaStream_t stream) {
-    return wide ? launch_one<QT, MODE, CG, 1>(args, grid, stream) : launch_one<QT, MODE, CG, 0>(args, grid, stream);
+    if (MODE == kBwd && args.nsplit > 1) return launch_one<QT, kBwd, CG, 0, 1>(args, grid, stream);
+    return wide ? launch_one<QT, MODE, CG, 1, 0>(args, grid, stream) : launch_one<QT, MODE, CG, 0, 0>(args, grid, stream);
 }
 
 // Most CTA pairs of this kernel that can be resident at once on the current device (0: pairs
@@ -74,13 +76,13 @@ static int max_pairs_one() {
         if (c != 0) return c > 0 ? c : 0;
     }
     int n = 0;
-    if (configure<QT, MODE, 2, 0>() == cudaSuccess) {   // both tile widths use the same threads and shared memory
+    if (configure<QT, MODE, 2, 0, 0>() == cudaSuccess) {   // both tile widths use the same threads and shared memory
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr;
         int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        fill_config<QT, MODE, 2, 0>(cfg, attr, sms & ~1, nullptr);
-        if (cudaOccupancyMaxActiveClusters(&n, mmq_gemm_kernel<QT, MODE, 2, 0>, &cfg) != cudaSuccess) {
+        fill_config<QT, MODE, 2, 0, 0>(cfg, attr, sms & ~1, nullptr);
+        if (cudaOccupancyMaxActiveClusters(&n, mmq_gemm_kernel<QT, MODE, 2, 0, 0>, &cfg) != cudaSuccess) {
             (void)cudaGetLastError();
             n = 0;
         }
