@@ -568,6 +568,7 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
         a.tasks = reinterpret_cast<const int4*>(static_cast<const uint8_t*>(p.ws) + 16);
         max_tasks = cap;
     }
+    if (max_tasks * mtiles * nsplit > INT32_MAX) return fail(TGO_E_ARG, "the problem has more than 2^31-1 tiles");
     int64_t grid = max_tasks * mtiles * nsplit;  // persistent CTAs (pairs) never outnumber the tiles
     if (grid > limit) grid = limit;
     if (grid < 1) grid = 1;
