@@ -282,4 +282,64 @@ __device__ __forceinline__ void decode32<QT_IQ2_S>(uint32_t blk, int g, uint32_t
     }
 }
 
+// decode64: weights 64s .. 64s+63 of a Q4_K / Q5_K block in one pass over the raw bytes they share
+// (one header load and one load of the 32 quant bytes instead of two of each): the first 32 come
+// back decoded, the last 32 as byte-sized quants with their scale and minimum, to be finished by
+// finish32 when the caller has room for them.  Same arithmetic as decode32, so the same bits.
+struct Pending32 {
+    uint32_t v[8];
+    float ds, dm;
+};
+__device__ __forceinline__ void finish32(const Pending32& p, uint4 (&out)[4]) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) out[c] = affine8(p.v[2 * c], p.v[2 * c + 1], p.ds, p.dm);
+}
+template <int QT>
+__device__ __forceinline__ void decode64(uint32_t blk, int s, uint4 (&out)[4], Pending32& p);
+
+template <>
+__device__ __forceinline__ void decode64<QT_Q4_K>(uint32_t blk, int s, uint4 (&out)[4], Pending32& p) {
+    const uint4 head = lds128(blk);
+    int sc0, mn0, sc1, mn1;
+    kquant_scale_min(head.y, head.z, head.w, 2 * s, sc0, mn0);
+    kquant_scale_min(head.y, head.z, head.w, 2 * s + 1, sc1, mn1);
+    const float d = half_bits_to_float(head.x & 0xFFFFu), dmin = half_bits_to_float(head.x >> 16);
+    const float ds0 = d * static_cast<float>(sc0), dm0 = dmin * static_cast<float>(mn0);
+    p.ds = d * static_cast<float>(sc1);
+    p.dm = dmin * static_cast<float>(mn1);
+    const uint32_t qs = blk + 16 + s * 32;
+    const uint4 a = lds128(qs), b = lds128(qs + 16);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) p.v[i] = (w[i] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) out[c] = affine8(w[2 * c] & 0x0F0F0F0Fu, w[2 * c + 1] & 0x0F0F0F0Fu, ds0, dm0);
+}
+
+template <>
+__device__ __forceinline__ void decode64<QT_Q5_K>(uint32_t blk, int s, uint4 (&out)[4], Pending32& p) {
+    const uint4 head = lds128(blk);
+    int sc0, mn0, sc1, mn1;
+    kquant_scale_min(head.y, head.z, head.w, 2 * s, sc0, mn0);
+    kquant_scale_min(head.y, head.z, head.w, 2 * s + 1, sc1, mn1);
+    const float d = half_bits_to_float(head.x & 0xFFFFu), dmin = half_bits_to_float(head.x >> 16);
+    const float ds0 = d * static_cast<float>(sc0), dm0 = dmin * static_cast<float>(mn0);
+    p.ds = d * static_cast<float>(sc1);
+    p.dm = dmin * static_cast<float>(mn1);
+    const uint4 ha = lds128(blk + 16), hb = lds128(blk + 32);
+    const uint32_t h[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+    const uint32_t qs = blk + 48 + s * 32;
+    const uint4 a = lds128(qs), b = lds128(qs + 16);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const int g = 2 * s;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) p.v[i] = ((w[i] >> 4) & 0x0F0F0F0Fu) | (((h[i] >> (g + 1)) & 0x01010101u) << 4);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t v0 = (w[2 * c] & 0x0F0F0F0Fu) | (((h[2 * c] >> g) & 0x01010101u) << 4);
+        const uint32_t v1 = (w[2 * c + 1] & 0x0F0F0F0Fu) | (((h[2 * c + 1] >> g) & 0x01010101u) << 4);
+        out[c] = affine8(v0, v1, ds0, dm0);
+    }
+}
+
 }  // namespace tgo

@@ -22,8 +22,8 @@
 // leader CTA (cluster rank 0) issues the UMMAs and owns the barriers both CTAs feed.
 //
 // Warp roles (768 threads): 0 activation producer (TMA), 1 UMMA issuer + TMEM owner, 2 raw
-// weight producer (TMA), 3 idle, 4-19 decode (two groups of 8 warps on alternate 64-element
-// steps), 20-23 epilogue (TMEM -> bf16 -> global).
+// weight producer (TMA), 3 idle, 4-19 decode (groups of warps on alternate 64-element steps: four
+// groups of 4 for Q4_K / Q5_K, two groups of 8 otherwise), 20-23 epilogue (TMEM -> bf16 -> global).
 //
 // Wide tiles.  A tile of more than 256 tokens (up to 512) is split into two halves that use both
 // accumulators at once and share every decoded weight step: each decoded stage is consumed by two
@@ -89,10 +89,13 @@ constexpr int kWgtTileBytes = kTileM * 128;
 #ifndef TGO_PAIR_RAW_STAGES_BWD
 #define TGO_PAIR_RAW_STAGES_BWD 4
 #endif
-constexpr int kDecodeWarps = 8;        // warps of one decode group (256 threads x 32 weights = one step)
-constexpr int kDecodeGroups = 2;       // groups take alternate steps, so two steps decode at once
+// Sixteen decode warps in groups that take alternate steps.  Block types whose blocks start 16-byte
+// aligned (Q4_K, Q5_K): four groups of four warps, a thread decodes the 64 weights of one row and
+// step, which share their quant bytes and scales (one pass over the raw bytes; half the
+// shared-memory loads).  The other types: two groups of eight warps, 32 weights per thread.
+constexpr int kDecodeWarpsAll = 16;
 constexpr int kFirstDecodeWarp = 4;
-constexpr int kFirstEpilogueWarp = kFirstDecodeWarp + kDecodeWarps * kDecodeGroups;  // multiple of 4
+constexpr int kFirstEpilogueWarp = kFirstDecodeWarp + kDecodeWarpsAll;  // multiple of 4
 #ifndef TGO_EPILOGUE_WARPS
 #define TGO_EPILOGUE_WARPS 4
 #endif
@@ -152,7 +155,9 @@ template <int QT, int MODE, int CG, int WIDE = 1>
 struct GemmCfg {
     using Fmt = BlockFmt<QT>;
     static constexpr int kSub = CG == 2 ? TGO_PAIR_SUBSTEPS : TGO_SUBSTEPS;   // steps per stage
-    static_assert(kSub == 1 || kSub == kDecodeGroups, "a stage holds one step, or one step per decode group");
+    static constexpr int kDecodeWarps = Fmt::kAligned ? 4 : 8;               // warps of one decode group (one step)
+    static constexpr int kDecodeGroups = kDecodeWarpsAll / kDecodeWarps;
+    static_assert(kDecodeGroups % kSub == 0 && 4 % kDecodeGroups == 0, "steps per stage / per block against decode groups");
     static constexpr int kActRows = kTileTok / CG;              // token rows staged by one CTA
     static constexpr int kActTileBytes = kActRows * 128;        // one step of activations
     static constexpr int kActSlots = CG == 2 ? TGO_PAIR_ACT_SLOTS : TGO_ACT_STAGES;          // steps of activations in flight
@@ -174,8 +179,9 @@ struct GemmCfg {
     static constexpr int kRawFit = 61440 / (kRawRows * Fmt::kBox);
     static constexpr int kRawMaxPair = MODE == kFwd ? TGO_PAIR_RAW_STAGES_FWD : TGO_PAIR_RAW_STAGES_BWD;
     static constexpr int kRawWanted = kRawFit >= kRawMaxPair ? kRawMaxPair : (kRawFit < 2 ? 2 : kRawFit);
-    static constexpr int kRawStages = CG == 2 ? (MODE == kBwd ? (kRawWanted & ~1) : kRawWanted)
+    static constexpr int kRawStages = CG == 2 ? (MODE == kBwd ? kRawWanted / kDecodeGroups * kDecodeGroups : kRawWanted)
                                               : (MODE == kFwd ? 2 : 4);
+    static_assert(kRawStages >= 2, "raw ring");
     static_assert(MODE == kFwd || kRawStages % kDecodeGroups == 0, "backward raw ring depth must be a multiple of the decode groups");
     static constexpr int kRawStageBytes = kRawRows * Fmt::kBox;
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
@@ -274,6 +280,8 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     // NAS / NBS: decoded-weight and activation slots (one step each); NB: stage barriers
     constexpr int NAS = Cfg::kWgtSlots, NBS = Cfg::kActSlots, NB = Cfg::kBars, NR = Cfg::kRawStages;
     constexpr int kActTileBytes = Cfg::kActTileBytes, KS = Cfg::kSub;
+    constexpr int kDecodeWarps = Cfg::kDecodeWarps, kDecodeGroups = Cfg::kDecodeGroups;
+    constexpr bool k64 = kDecodeWarps == 4;   // a decode thread takes 64 weights (one row of a step)
     // CTA pair: rank 0 (the leader) owns the barriers both CTAs feed (full, acc_empty) and issues
     // the UMMAs; every CTA owns the barriers only it waits on (done, raw, acc_full).
     const int rank = CG == 2 ? static_cast<int>(cluster_ctarank()) : 0;
@@ -608,11 +616,11 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     } else if (warp >= kFirstDecodeWarp && warp < kFirstEpilogueWarp) {
         // ------------------------------------------------------------ decode warps
         // Group g decodes the steps whose running index is g (mod kDecodeGroups).  Forward: one raw
-        // stage (a super-block column of 128 rows) serves four steps, two per group; a thread
+        // stage (a super-block column of 128 rows) serves four steps, shared out over the groups; a thread
         // keeps its row and 32-weight half for the whole tile.  Backward: one raw stage (64 rows)
         // per step; a thread keeps its row slot and 32-weight group.
         const int group = (warp - kFirstDecodeWarp) / kDecodeWarps;
-        const int dt = threadIdx.x - (kFirstDecodeWarp + group * kDecodeWarps) * 32;  // 0..255
+        const int dt = threadIdx.x - (kFirstDecodeWarp + group * kDecodeWarps) * 32;  // 0 .. 32 * kDecodeWarps - 1
         // Forward: 128 rows x 2 halves, (row, half) = (dt / 2, dt % 2).  Backward: 64 rows x 4
         // quarters.  For the 16-byte-aligned block types (128-bit loads) (row, quarter) =
         // (dt % 64, dt / 64): a quarter-warp, which shares one 128-bit store wavefront, then holds
@@ -621,16 +629,23 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
         // 64-column halves of the image are 8 KB apart).  The other types read their blocks as
         // 32-bit words, many of them common to the four quarters of a row: there (dt / 4, dt % 4)
         // keeps those loads broadcasts and the eight rows of a warp on different banks.
+        // 64 weights per thread (aligned types): forward 128 rows, thread = row; backward 64 rows x
+        // the two 64-column halves of the CTA's 128 in-features, (row, half) = (dt % 64, dt / 64).
+        // Either way a quarter-warp holds eight consecutive rows, whose raw blocks (128-bit loads)
+        // and swizzled chunks (128-bit stores) cover all banks.
         constexpr bool kRowMajorLanes = MODE == kBwd && Fmt::kAligned;
-        const int row = MODE == kFwd ? dt >> 1 : (kRowMajorLanes ? dt & 63 : dt >> 2);   // weight row inside the raw stage
-        const int sub = MODE == kFwd ? dt & 1 : (kRowMajorLanes ? dt >> 6 : dt & 3);     // which 32 weights of the step's span
-        // byte offsets of this thread's four 16-byte chunks inside a decoded tile (128B swizzle)
-        uint32_t coff[4];
+        const int row = k64 ? (MODE == kFwd ? dt : dt & 63)
+                            : (MODE == kFwd ? dt >> 1 : (kRowMajorLanes ? dt & 63 : dt >> 2));   // weight row inside the raw stage
+        const int sub = k64 ? (MODE == kFwd ? 0 : 2 * (dt >> 6))
+                            : (MODE == kFwd ? dt & 1 : (kRowMajorLanes ? dt >> 6 : dt & 3));     // first 32-weight group of the step's span
+        // byte offsets of this thread's 16-byte chunks inside a decoded tile (128B swizzle)
+        constexpr int kChunks = k64 ? 8 : 4;
+        uint32_t coff[kChunks];
         {
             const uint32_t base = (MODE == kFwd ? 0u : static_cast<uint32_t>(sub >> 1) * 8192u) + row * 128u;
             const int cbase = 4 * (sub & 1);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) coff[c] = base + (((cbase + c) ^ (row & 7)) << 4);
+            for (int c = 0; c < kChunks; ++c) coff[c] = base + (((cbase + c) ^ (row & 7)) << 4);
         }
         const int P = args.wgt_classes, lgP = args.wgt_classes_log2;
         // Running state of this group.  A decoded step is read by pipeline stage `stg` (and by
@@ -670,10 +685,23 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             // an arrival) is short.  The slot's credit loop - the latency that sets the stage time -
             // no longer contains the decode.
             uint4 o[4];
-            if (valid) {
-                decode32<QT>(blk, g, grid_s, o);
+            Pending32 rest;   // 64 weights per thread: the last 32 stay byte-sized quants until the first 32 are stored
+            if constexpr (k64) {
+                if (valid) {
+                    decode64<QT>(blk, g >> 1, o, rest);
+                } else {
+                    o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) rest.v[i] = 0u;
+                    rest.ds = 0.0f;
+                    rest.dm = 0.0f;
+                }
             } else {
-                o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
+                if (valid) {
+                    decode32<QT>(blk, g, grid_s, o);
+                } else {
+                    o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u);
+                }
             }
             if (raw_bar_to_release != 0) {   // the raw blocks are in registers now: hand the raw stage back early
                 __syncwarp();
@@ -691,6 +719,11 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             const uint32_t tile_s = wgt_s + (WIDE ? slot_off : (it % NAS) * kWgtTileBytes);
 #pragma unroll
             for (int c = 0; c < 4; ++c) sts128(tile_s + coff[c], o[c]);
+            if constexpr (k64) {
+                finish32(rest, o);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) sts128(tile_s + coff[4 + c], o[c]);
+            }
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -701,7 +734,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             }
             it += kDecodeGroups;
             if (WIDE) {
-                slot_off += kDecodeGroups * kWgtTileBytes;
+                slot_off += (kDecodeGroups % NAS) * kWgtTileBytes;
                 if (slot_off >= kSlotWrap) slot_off -= kSlotWrap;
                 stg += stg_inc;
                 jw += static_cast<int>(stg_inc);
@@ -737,9 +770,10 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                     const uint32_t r = raw_it % NR, rph = (raw_it / NR) & 1u;
                     if (!all_wait(bar_raw_full + 8 * r, rph, abort_word, kAbortRawFull)) { ok = false; break; }
                     const uint32_t blk = blk0 + r * Cfg::kRawStageBytes + (Fmt::kAligned ? 0 : (mis0 + kb * Fmt::kBytes) & 15);
+                    constexpr int kPerBlock = 4 / kDecodeGroups;   // steps of a block column that one group decodes
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        if (!emit(blk, 2 * (group + 2 * u) + sub, row_ok, u == 1 ? bar_raw_empty + 8 * r : 0u)) { ok = false; break; }
+                    for (int u = 0; u < kPerBlock; ++u) {
+                        if (!emit(blk, 2 * (group + kDecodeGroups * u) + sub, row_ok, u == kPerBlock - 1 ? bar_raw_empty + 8 * r : 0u)) { ok = false; break; }
                     }
                 }
             } else {
@@ -800,24 +834,34 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 }
             } else if ((mdim & 7) == 0 && mq + 32 <= mdim) {
                 // Transposing path: the warp's 32 outputs x 16 tokens go through a private staging
-                // tile [token][32 outputs] so that global stores are 16 bytes per lane.
+                // tile so that global stores are 16 bytes per lane.  The tile holds token pairs:
+                // row p = tokens 2p, 2p + 1, one 4-byte word per output (one conversion and one
+                // conflict-free store per two accumulator values); the 16-byte chunks of a row are
+                // XOR-swizzled with the row's parity so that the 128-bit reads of two rows at a
+                // time are conflict-free as well.  A lane then unzips 8 outputs of both tokens.
                 uint8_t* stage = epi_g + (warp - kFirstEpilogueWarp) * (16 * 64);
+                const int wchunk = lane >> 2, wword = (lane & 3) << 2;
+                const int p = lane >> 2, part = lane & 3;
+                const uint8_t* rd0 = stage + p * 128 + (((2 * part) ^ (p & 1)) << 4);
+                const uint8_t* rd1 = stage + p * 128 + (((2 * part + 1) ^ (p & 1)) << 4);
                 for (int c0 = 16 * ehalf; c0 < ntok_pad; c0 += 4 * kEpilogueWarps) {
                     uint32_t v[16];
                     tmem_ld16(taddr + c0, v);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        *reinterpret_cast<__nv_bfloat16*>(stage + j * 64 + lane * 2) =
-                            __float2bfloat16(__uint_as_float(v[j]));
+                    for (int q = 0; q < 8; ++q)
+                        *reinterpret_cast<uint32_t*>(stage + q * 128 + (((wchunk ^ (q & 1)) << 4) | wword)) =
+                            pack_bf16(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
                     __syncwarp();
-#pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const int r = (lane >> 2) + 8 * i, part = lane & 3;
-                        const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 64 + part * 16);
-                        if (c0 + r < ntok)
-                            *reinterpret_cast<uint4*>(out_base + static_cast<long long>(c0 + r) * mdim + mq + part * 8) = val;
-                    }
+                    const uint4 a = *reinterpret_cast<const uint4*>(rd0);
+                    const uint4 b = *reinterpret_cast<const uint4*>(rd1);
+                    __nv_bfloat16* dst = out_base + static_cast<long long>(c0 + 2 * p) * mdim + mq + part * 8;
+                    if (c0 + 2 * p < ntok)
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410),
+                                                                    __byte_perm(b.x, b.y, 0x5410), __byte_perm(b.z, b.w, 0x5410));
+                    if (c0 + 2 * p + 1 < ntok)
+                        *reinterpret_cast<uint4*>(dst + mdim) = make_uint4(__byte_perm(a.x, a.y, 0x7632), __byte_perm(a.z, a.w, 0x7632),
+                                                                           __byte_perm(b.x, b.y, 0x7632), __byte_perm(b.z, b.w, 0x7632));
                     __syncwarp();
                 }
             } else {
