@@ -21,8 +21,9 @@
 // cta_group::2 UMMAs; each CTA decodes its own 128 rows and stages half of the tokens, the
 // leader CTA (cluster rank 0) issues the UMMAs and owns the barriers both CTAs feed.
 //
-// Warp roles (768 threads): 0 activation producer (TMA), 1 UMMA issuer + TMEM owner, 2 raw
-// weight producer (TMA), 3 idle, 4-19 decode (groups of warps on alternate 64-element steps: four
+// Warp roles (768 threads; backward - forward places them differently, see the kernel): 0 activation
+// producer (TMA), 1 UMMA issuer + TMEM owner, 2 and 3 raw weight producers (TMA, alternate stages),
+// 4-19 decode (groups of warps on alternate 64-element steps: four
 // groups of 4 for Q4_K / Q5_K, two groups of 8 otherwise), 20-23 epilogue (TMEM -> bf16 -> global).
 //
 // Wide tiles.  A tile of more than 256 tokens (up to 512) is split into two halves that use both
@@ -181,7 +182,7 @@ struct GemmCfg {
     static constexpr int kRawWanted = kRawFit >= kRawMaxPair ? kRawMaxPair : (kRawFit < 2 ? 2 : kRawFit);
     static constexpr int kRawStages = CG == 2 ? (MODE == kBwd ? kRawWanted / kDecodeGroups * kDecodeGroups : kRawWanted)
                                               : (MODE == kFwd ? 2 : 4);
-    static_assert(kRawStages >= 2, "raw ring");
+    static_assert(kRawStages >= 2 && kRawStages % 2 == 0, "raw ring: two producers take alternate stages");
     static_assert(MODE == kFwd || kRawStages % kDecodeGroups == 0, "backward raw ring depth must be a multiple of the decode groups");
     static constexpr int kRawStageBytes = kRawRows * Fmt::kBox;
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
@@ -371,7 +372,19 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
     const uint32_t lead_full = CG == 2 ? map_to_cta(bar_full, 0) : bar_full;
     const uint32_t lead_acc_empty = CG == 2 ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
 
-    if (warp == 0) {
+    // Warp roles.  Backward: warps 0 / 2 / 3 are the activation and the two raw-weight producers,
+    // 4-19 decode.  Forward: the three single-thread roles whose serial instruction streams set the
+    // pace there (UMMA issuer 1, activation producer 5, raw producers 9 and 13) share scheduler
+    // partition 1 with one decode warp and one epilogue warp, so that they compete for issue slots
+    // with two busy warps instead of five; the other partitions take five decode warps each.
+    // Measured on the benchmark (Q4_K, 256 ragged groups): forward +3 %; backward, whose short
+    // tiles keep the epilogue warps busy, loses with that placement and keeps the plain one.
+    constexpr bool kRemap = MODE == kFwd;
+    constexpr int kActWarp = kRemap ? 5 : 0, kRawWarp = kRemap ? 9 : 2, kRawWarp2 = kRemap ? 13 : 3;
+    const bool light = kRemap ? ((warp & 3) == 1 && warp < 16) : warp < kFirstDecodeWarp;
+    // decode warp index 0..15
+    const int dwarp = kRemap ? warp - ((warp > 1) + (warp > 5) + (warp > 9) + (warp > 13)) : warp - kFirstDecodeWarp;
+    if (warp == kActWarp) {
         // ------------------------------------------------------------ activation producer
         // One pipeline stage = KS one-step slots of the tokens of one half.  `it` is the running
         // pipeline-stage index; stage it uses slots it * KS .. it * KS + KS - 1 (mod NBS).
@@ -379,51 +392,76 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             if (lane == 0) {
                 for (int s = 0; s < args.nsets; ++s)
                     for (int b = 0; b < kNumBoxes; ++b) prefetch_tmap(&args.act_maps[s].box[b]);
-                uint32_t it = 0;
+                // This thread's loop is one of the serial chains that set the pace, so everything
+                // it needs per stage is a running value: the stage's barrier, the barrier of the
+                // stage whose slots it refills (D stages back), the ring slot, and the position in
+                // the reduction.  The token rows of a half are fetched with the boxes whose heights
+                // are the binary digits of the row count (a multiple of 16).
+                constexpr uint32_t D = NBS / KS;            // stage it refills the last slot of stage it - D
+                uint32_t it = 0;                            // running pipeline stage
+                uint32_t full_off = 0;                      // 8 * (it % NB)
+                uint32_t wait_off = 0, wait_ph = 0;         // barrier and phase of stage it - D
+                uint32_t slot = 0;                          // (it * KS) % NBS
                 bool ok = true;
                 for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                     TileInfo t;
                     if (!load_tile<MODE, CG, WIDE, SPLIT>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
+                    int rem_h[2], row_h[2];
+#pragma unroll
+                    for (int h = 0; h < (WIDE ? 2 : 1); ++h) {
+                        rem_h[h] = pad_tokens<CG>(half_tokens(t, h)) / CG;
+                        row_h[h] = half_row0(t, h) + rank * rem_h[h];
+                    }
+                    // position of the tile's next decoded stage in the reduction
+                    int step = 0;
+                    int astep = SPLIT ? t.split * nsteps : 0;
+                    int set = 0, red0 = MODE == kFwd ? 0 : astep * kStepK;
+                    if (MODE == kBwd && SPLIT) {
+                        set = astep / steps_set;
+                        red0 = (astep - set * steps_set) * kStepK;
+                    }
                     const int npipe = nstages * t.nhalf;
                     for (int ps = 0; ps < npipe; ++ps, ++it) {
-                        const int stage = t.nhalf == 2 ? ps >> 1 : ps;
-                        const int half = t.nhalf == 2 ? ps & 1 : 0;
-                        const int hpad = pad_tokens<CG>(half_tokens(t, half));
-                        const uint32_t s = it % NB;
-                        // the stage's last step reuses the slot of step (last - NBS): wait for that stage's UMMAs
-                        const uint32_t last = it * KS + (KS - 1);
-                        if (last >= static_cast<uint32_t>(NBS)) {
-                            const uint32_t jw = (last - NBS) / KS;
-                            if (!mbar_wait(bar_done + 8 * (jw % NB), (jw / NB) & 1u, abort_word, kAbortActEmpty)) { ok = false; break; }
+                        const int half = (WIDE && t.nhalf == 2) ? ps & 1 : 0;
+                        const bool last_half = !(WIDE && t.nhalf == 2) || half == 1;
+                        const int rem = rem_h[WIDE ? half : 0], row0 = row_h[WIDE ? half : 0];
+                        if (it >= D) {
+                            if (!mbar_wait(bar_done + wait_off, wait_ph, abort_word, kAbortActEmpty)) { ok = false; break; }
+                            wait_off += 8;
+                            if (wait_off == 8 * NB) { wait_off = 0; wait_ph ^= 1u; }
                         }
                         // the leader announces the bytes of the whole stage; each CTA copies its share
                         // of the token rows (all of them, or its half) and the bytes count on the
                         // leader's barrier
-                        const uint32_t bar = lead_full + 8 * s;
-                        if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, static_cast<uint32_t>(hpad) * 128u * KS);
+                        const uint32_t bar = lead_full + full_off;
+                        if (rank == 0) mbar_arrive_expect_tx(bar_full + full_off, static_cast<uint32_t>(rem * CG) * 128u * KS);
+                        int s_step = step, s_astep = astep, s_set = set, s_red = red0;
 #pragma unroll
                         for (int ks = 0; ks < KS; ++ks) {
-                            const int step = stage * KS + ks;
-                            const int astep = SPLIT ? t.split * nsteps + step : step;   // step of the whole reduction
-                            int set = MODE == kFwd ? 0 : astep / steps_set;
                             // a step past the end reads columns outside the matrix: TMA fills zeros
-                            int red0 = (MODE == kFwd ? step : astep - set * steps_set) * kStepK;
-                            if (step >= nsteps || astep >= steps_all) { set = 0; red0 = (steps_set + 1) * kStepK; }
-                            uint32_t dst = act_s + ((it * KS + ks) % NBS) * kActTileBytes;
-                            int rem = hpad / CG;
-                            int row = half_row0(t, half) + rank * rem;
+                            const bool past = s_step >= nsteps || s_astep >= steps_all;
+                            const int use_set = past ? 0 : s_set;
+                            const int col = past ? (steps_set + 1) * kStepK : s_red;
+                            const uint32_t dst = act_s + slot * kActTileBytes;
 #pragma unroll
                             for (int b = 0; b < kNumBoxes; ++b) {
+                                constexpr int kAll = 2 * Cfg::kActRows - 1;
                                 const int h = 256 >> b;
-                                if (h <= Cfg::kActRows && rem >= h) {
-                                    if (CG == 2) tma_load_2d_pair(dst, &args.act_maps[set].box[b], bar, red0, row);
-                                    else tma_load_2d(dst, &args.act_maps[set].box[b], bar, red0, row);
-                                    dst += h * 128;
-                                    row += h;
-                                    rem -= h;
+                                if (h <= Cfg::kActRows && (rem & h) != 0) {
+                                    const int off = rem & (kAll & ~(2 * h - 1));   // rows taken by the taller boxes
+                                    if (CG == 2) tma_load_2d_pair(dst + off * 128, &args.act_maps[use_set].box[b], bar, col, row0 + off);
+                                    else tma_load_2d(dst + off * 128, &args.act_maps[use_set].box[b], bar, col, row0 + off);
                                 }
                             }
+                            if (++slot == NBS) slot = 0;
+                            ++s_step;
+                            ++s_astep;
+                            s_red += kStepK;
+                            if (MODE == kBwd && s_red >= steps_set * kStepK) { s_red = 0; ++s_set; }
                         }
+                        if (last_half) { step = s_step; astep = s_astep; set = s_set; red0 = s_red; }
+                        full_off += 8;
+                        if (full_off == 8 * NB) full_off = 0;
                     }
                 }
             }
@@ -573,9 +611,13 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
                 tl += static_cast<uint32_t>(nhalf);
             }
         }
-    } else if (warp == 2) {
+    } else if (warp == kRawWarp || warp == kRawWarp2) {
         // ------------------------------------------------------------ raw weight producer
         // One box load per alignment class and stage: rows / P block windows of kBox bytes each.
+        // Two producer threads (in different warps) take alternate raw stages: one thread needs
+        // some 900 cycles per stage (a wait, an expect_tx, the copies, each a shared-memory or TMA
+        // round trip under load), which backward - one raw stage per 64-element step - set the pace.
+        const uint32_t my_parity = warp == kRawWarp ? 0u : 1u;
         if (lane == 0) {
             uint32_t itr = 0;
             bool ok = true;
@@ -583,44 +625,80 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             constexpr int kRows = Cfg::kRawRows;
             for (int s = 0; s < args.nsets; ++s)
                 for (int c = 0; c < P; ++c) prefetch_tmap(&args.wgt_maps[s].cls[c]);
+            // Everything that does not change from one raw stage to the next is worked out once
+            // per tile: this thread's loop is one of the serial chains that set the pace backward
+            // (one raw stage per 64-element step).  Per alignment class c: the box's byte column x
+            // (backward: fixed for the tile; forward: advances by one block per stage) and the row
+            // index inside map c of the tile's first weight row.  A step is 64 rows and P divides
+            // 64, so the class of a row and the rows' order inside a stage never change.
+            const uint32_t tx_bytes = static_cast<uint32_t>(kRows) * Fmt::kBox;
+            const int rows_per_class = kRows >> lgP;
             for (long long tile = cta; ok && tile < total_tiles; tile += ncta) {
                 TileInfo t;
                 if (!load_tile<MODE, CG, WIDE, SPLIT>(args, static_cast<int>(tile), mtiles, mtiles_set, rank, t)) continue;
                 const int nraw = MODE == kFwd ? nkb : nsteps_pad;
+                const long long gbase = static_cast<long long>(t.expert) * N + (MODE == kFwd ? t.m0 : 0);
+                int y0[kMaxWgtClasses], x0[kMaxWgtClasses];
+#pragma unroll
+                for (int c = 0; c < kMaxWgtClasses; ++c) {
+                    if (c < P) {
+                        const long long first = gbase + ((c - gbase) & (P - 1));   // first row of class c at or after the base
+                        y0[c] = static_cast<int>((first - c) >> lgP);
+                        const int mis_c = (c * args.wgt_row_bytes) & 15;
+                        x0[c] = mis_c + (MODE == kFwd ? 0 : (t.m0 >> 8) * Fmt::kBytes);
+                    }
+                }
+                // backward: running position in the reduction (weight set, first out-feature of the step)
+                int set = MODE == kFwd ? t.set : 0, n_first = 0;
+                if (SPLIT) {
+                    const int astep0 = t.split * nsteps;
+                    set = astep0 / steps_set;
+                    n_first = (astep0 - set * steps_set) * kStepK;
+                }
+                int astep = SPLIT ? t.split * nsteps : 0;
                 for (int ri = 0; ri < nraw; ++ri, ++itr) {
+                    if ((itr & 1u) != my_parity) {   // the other producer's stage
+                        if (MODE == kBwd) {
+                            ++astep;
+                            n_first += kStepK;
+                            if (n_first >= steps_set * kStepK) { n_first = 0; ++set; }
+                        }
+                        continue;
+                    }
                     const uint32_t r = itr % NR, ph = (itr / NR) & 1u;
                     if (!mbar_wait(bar_raw_empty + 8 * r, ph ^ 1u, abort_word, kAbortRawEmpty)) { ok = false; break; }
-                    int set, n_first, kb;
+                    int use_set = set, yoff = 0, xoff = 0;
                     if (MODE == kFwd) {
-                        set = t.set; n_first = t.m0; kb = ri;
+                        xoff = ri * Fmt::kBytes;
                     } else {
-                        const int astep = SPLIT ? t.split * nsteps + ri : ri;
-                        set = astep / steps_set; n_first = (astep - set * steps_set) * kStepK; kb = t.m0 >> 8;
-                        if (ri >= nsteps || astep >= steps_all) { set = 0; n_first = 0; }   // a step past the end: decoded as zeros
+                        yoff = n_first >> lgP;
+                        if (ri >= nsteps || astep >= steps_all) { use_set = 0; yoff = 0; }   // a step past the end: decoded as zeros
                     }
-                    const long long g0 = static_cast<long long>(t.expert) * N + n_first;  // first global weight row
                     const uint32_t bar = bar_raw_full + 8 * r;
-                    mbar_arrive_expect_tx(bar, static_cast<uint32_t>(kRows) * Fmt::kBox);
+                    mbar_arrive_expect_tx(bar, tx_bytes);
                     const uint32_t stage_s = raw_s + r * Cfg::kRawStageBytes;
-                    for (int c = 0; c < P; ++c) {
-                        // first row of class c at or after g0, as a row index inside map c
-                        const long long first = g0 + ((c - g0) & (P - 1));
-                        const int y = static_cast<int>((first - c) >> lgP);
-                        const int mis_c = (c * args.wgt_row_bytes) & 15;
-                        const int x = (mis_c + kb * Fmt::kBytes) & ~15;
-                        tma_load_2d(stage_s + c * (kRows >> lgP) * Fmt::kBox, &args.wgt_maps[set].cls[c], bar, x, y);
+#pragma unroll
+                    for (int c = 0; c < kMaxWgtClasses; ++c) {
+                        if (c < P)
+                            tma_load_2d(stage_s + c * rows_per_class * Fmt::kBox, &args.wgt_maps[use_set].cls[c], bar,
+                                        (x0[c] + xoff) & ~15, y0[c] + yoff);
+                    }
+                    if (MODE == kBwd) {
+                        ++astep;
+                        n_first += kStepK;
+                        if (n_first >= steps_set * kStepK) { n_first = 0; ++set; }
                     }
                 }
             }
         }
-    } else if (warp >= kFirstDecodeWarp && warp < kFirstEpilogueWarp) {
+    } else if (!light && warp < kFirstEpilogueWarp) {
         // ------------------------------------------------------------ decode warps
         // Group g decodes the steps whose running index is g (mod kDecodeGroups).  Forward: one raw
         // stage (a super-block column of 128 rows) serves four steps, shared out over the groups; a thread
         // keeps its row and 32-weight half for the whole tile.  Backward: one raw stage (64 rows)
         // per step; a thread keeps its row slot and 32-weight group.
-        const int group = (warp - kFirstDecodeWarp) / kDecodeWarps;
-        const int dt = threadIdx.x - (kFirstDecodeWarp + group * kDecodeWarps) * 32;  // 0 .. 32 * kDecodeWarps - 1
+        const int group = dwarp / kDecodeWarps;
+        const int dt = (dwarp % kDecodeWarps) * 32 + lane;  // 0 .. 32 * kDecodeWarps - 1
         // Forward: 128 rows x 2 halves, (row, half) = (dt / 2, dt % 2).  Backward: 64 rows x 4
         // quarters.  For the 16-byte-aligned block types (128-bit loads) (row, quarter) =
         // (dt % 64, dt / 64): a quarter-warp, which shares one 128-bit store wavefront, then holds
