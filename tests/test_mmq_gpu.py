@@ -36,6 +36,31 @@ def test_forward_and_grad_input_through_the_c_abi(cuda, name, qt, M, N, K):
 
 
 @pytest.mark.parametrize("name,qt", ALL_TYPES)
+@pytest.mark.parametrize("wide", ["0", "1"])
+def test_identity_activations_return_the_dequantised_weights(cuda, monkeypatch, name, qt, wide):
+    """x = I gives y[t, n] = W[n, t] and dy = I gives dx[t, k] = W[t, k], both exactly: every
+    output is one product by 1.0 plus zeros.  This pins the decoders inside the matmul kernel
+    (all groups, rows and chunks, both operand orientations, both tile widths) against the
+    stand-alone dequantiser, which the oracle tests pin bit for bit."""
+    from torch_ggml_ops_b200 import native
+
+    monkeypatch.setenv("TGO_WIDE_TILES", wide)
+    N, K = 384, 512
+    w, _, _ = dense_case(qt, N, K, 300 + qt)
+    wd = to_dev(w)
+    Wb = native.dequantize_bf16(wd.reshape(-1), qt).reshape(N, K)
+    eye_k = torch.eye(K, dtype=torch.bfloat16, device="cuda")
+    y = torch.full((K, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    native.mmq_fwd(eye_k, wd, y, K, N, K, qt)
+    assert values_equal(y, Wb.t())
+    eye_n = torch.eye(N, dtype=torch.bfloat16, device="cuda")
+    dx = torch.full((N, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+    native.mmq_dx(eye_n, wd, dx, N, N, K, qt)
+    assert values_equal(dx, Wb)
+    assert native.device_status() == 0
+
+
+@pytest.mark.parametrize("name,qt", ALL_TYPES)
 def test_golden_known_answers(cuda, golden, name, qt):
     import torch_ggml_ops_b200 as tgo
 
