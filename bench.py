@@ -364,11 +364,14 @@ def gpu_arm(args):
     y_out = [torch.empty(R, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]
     dx_out = [torch.empty(T, K, dtype=torch.bfloat16, device=dev) for _ in range(2)]
 
-    def step_ep(x=x_tok, dy=dy_rows, b=0):
+    def step_ep(x=x_tok, dy=dy_rows, b=0, keep=False):
+        """One step.  The forward rows arrive in this rank's peer-addressable result buffer (the
+        matmul epilogues of the experts' GPUs store them there); ``keep`` copies them to a private
+        buffer, for a reader that overlaps the next step (the end-to-end loop's copy-out stream)."""
         plan = pep.plan(ids32)
-        pep.forward(plan, x, out=y_out[b])
+        y = pep.forward(plan, x, out=y_out[b] if keep else None)
         pep.grad_input(plan, dy, out=dx_out[b])
-        return y_out[b], dx_out[b]
+        return y, dx_out[b]
 
     result = {}
     if not args.profile:
@@ -486,7 +489,7 @@ def gpu_arm(args):
         with torch.cuda.stream(s_cmp):
             s_cmp.wait_event(ev_in[b])
             s_cmp.wait_event(ev_out[b])         # the copy-out that last read these output buffers is done
-            step_ep(xd[b], dyd[b], b)
+            step_ep(xd[b], dyd[b], b, keep=True)
             ev_cmp[b].record(s_cmp)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_cmp[b])

@@ -137,6 +137,19 @@ int tgo_grouped_fwd(const void* x, const void* w0, const void* w1, void* y0, voi
                     int64_t in_features, int quant_type, void* workspace, int64_t workspace_bytes,
                     void* stream);
 
+/* The same forward (one projection) with scattered output rows: row r of the result is stored at
+ * y_rows[r] (a device array of `rows` addresses, each 16-byte aligned and writable by this GPU -
+ * its own memory or a peer's; null drops the row) instead of a contiguous [rows][out_features]
+ * tensor.  The matmul kernel's epilogue stores straight there, so an expert-parallel step can
+ * return every routed pair's row to the GPU that owns the token from inside the matmul
+ * (tgo_ep_row_pointers builds the table).  out_features must be a multiple of 8.  Values are
+ * bit-identical to tgo_grouped_fwd.  No counterpart in the reference (it is single-GPU). */
+int tgo_grouped_fwd_rows(const void* x, const void* w, void* const* y_rows,
+                         const int64_t* expert_indices, const int32_t* expert_offsets,
+                         int64_t num_groups, int64_t num_experts, int64_t rows,
+                         int64_t out_features, int64_t in_features, int quant_type,
+                         void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Grouped input gradient dX = dY0*W0[e] (+ dY1*W1[e] when dy1/w1 are non-null; both products
  * are summed in fp32 before the single bf16 rounding).
  * Replaces grouped_mmq_grad_input_cuda and grouped_mmq_pair_grad_input_cuda
@@ -249,6 +262,13 @@ int tgo_ep_pull(void* const* peer_ptrs, int64_t world, const int32_t* dst_rank, 
  *  tgo_ep_expand          owner side: rows[row] = token_buffer[row_slot[row]] for row < *n_rows_device
  *                         (a device int32, e.g. the last cumulative offset of tgo_ep_plan); a row whose
  *                         entry is outside [0, n_slots) is left untouched;
+ *  tgo_ep_row_pointers    owner side, for tgo_grouped_fwd_rows: row_ptrs[row] = result_ptrs[owner] + (token * top_k
+ *                         + s) * width * 2 for the routed pair (slot = owner * tokens_per_rank + token, s) that row
+ *                         belongs to (found through row_slot and slot_rows), null for a row nobody announced;
+ *                         result_ptrs are this GPU's addresses of every rank's [tokens_per_rank * top_k][width]
+ *                         result buffer;
+ *  tgo_ep_zero_dropped    token owner's side of that scheme: zeroes result[i] for the routed pairs with
+ *                         dst_rank[i] < 0 (dropped for lack of room), which nobody else writes;
  *  tgo_ep_reduce          owner side: partial_sums[slot] = sum of rows[slot_rows[slot][s]] (fp32, one rounding);
  *  tgo_ep_pull_tokens     out[t] = sum over the GPUs owning one of t's experts of their partial_sums[slot]. */
 int tgo_ep_token_maps(const int32_t* dst_rank, const int32_t* dst_row, int64_t tokens, int64_t top_k,
@@ -261,6 +281,12 @@ int tgo_ep_dispatch_tokens(const void* src, const int32_t* dst_rank, int64_t tok
 int tgo_ep_expand(const void* token_buffer, int64_t n_slots, const int32_t* row_slot,
                   const int32_t* n_rows_device, void* rows, int64_t capacity, int64_t width,
                   void* stream);
+int tgo_ep_zero_dropped(const int32_t* dst_rank, int64_t n_pairs, void* result, int64_t width,
+                        void* stream);
+int tgo_ep_row_pointers(const int32_t* row_slot, const int32_t* slot_rows, const int32_t* n_rows_device,
+                        int64_t capacity, int64_t n_slots, int64_t top_k, int64_t tokens_per_rank,
+                        void* const* result_ptrs, int64_t world, int64_t width, void** row_ptrs,
+                        void* stream);
 int tgo_ep_reduce(const void* rows, const int32_t* slot_rows, int64_t n_slots, int64_t top_k,
                   void* partial_sums, int64_t width, void* stream);
 int tgo_ep_pull_tokens(void* const* partial_sum_ptrs, int64_t world, const int32_t* dst_rank,

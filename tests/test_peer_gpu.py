@@ -97,7 +97,69 @@ def test_virtual_ranks_dispatch_matmul_pull(cuda, world):
             want_dx[i // top_k] += gate.reshape(-1)[i] * (dys[r][i].float() @ W[f[i]])
         assert ref.rel_frobenius(y.float().cpu(), want_y) < FWD_TOL
         assert ref.rel_frobenius(dx.float().cpu(), want_dx) < DX_TOL
+    # forward with scattered output rows: every owner's matmul epilogue stores each row straight into
+    # the result buffer of the rank that owns the token; bit-identical to compute-then-pull
+    y_tok = [torch.full((tokens * top_k, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    for o in range(world):
+        row_ptrs = torch.full((cap,), -1, dtype=torch.int64, device="cuda")
+        native.ep_row_pointers(row_slot[o], slot_rows[o], plans[o][3][EL - 1:], top_k, tokens, ptrs(y_tok), N, row_ptrs)
+        ws = torch.empty(native.grouped_workspace_bytes(cap, EL), dtype=torch.uint8, device="cuda")
+        wl = wdev[o * EL:(o + 1) * EL].contiguous()
+        native.grouped_fwd_rows(x_in[o], wl, row_ptrs, plans[o][2], plans[o][3], EL, cap, N, K, qt, ws)
+    for r in range(world):
+        y = torch.empty(tokens * top_k, N, dtype=torch.bfloat16, device="cuda")
+        native.ep_pull(ptrs(y_out), plans[r][0], plans[r][1], y, 1)
+        torch.cuda.synchronize()
+        assert np.array_equal(bits(y_tok[r]), bits(y))
     assert native.device_status() == 0
+
+
+@pytest.mark.parametrize("N", [64, 72, 200])
+def test_scattered_rows_null_pointers_and_odd_widths(cuda, N):
+    """tgo_grouped_fwd_rows on its own: rows go to a permuted destination, a null entry drops its row,
+    out-feature counts that leave a partial last tile of weight rows take the element-wise path."""
+    from torch_ggml_ops_b200 import native
+
+    qt, E, K, sizes = ref.Q4_K, 3, 256, [70, 0, 300]
+    w = blocks.expert_weights(qt, E, N, K, 8)
+    R = sum(sizes)
+    eo = to_dev(torch.tensor(np.cumsum(sizes), dtype=torch.int32))
+    ei = to_dev(torch.arange(E, dtype=torch.int64))
+    x = to_dev(blocks.gaussian_bf16((R, K), 9))
+    ws = torch.empty(native.grouped_workspace_bytes(R, E), dtype=torch.uint8, device="cuda")
+    y = torch.empty(R, N, dtype=torch.bfloat16, device="cuda")
+    native.grouped_fwd(x, to_dev(w), None, y, None, ei, eo, E, R, N, K, qt, ws)
+    perm = torch.randperm(R, generator=torch.Generator().manual_seed(3))
+    dst = torch.full((R, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ptr = dst.data_ptr() + perm.to(torch.int64) * (N * 2)
+    dropped = torch.arange(R) % 7 == 3
+    ptr[dropped] = 0
+    native.grouped_fwd_rows(x, to_dev(w), to_dev(ptr), ei, eo, E, R, N, K, qt, ws)
+    torch.cuda.synchronize()
+    got = dst.cpu()
+    keep = ~dropped
+    assert np.array_equal(bits(got[perm[keep]]), bits(y.cpu()[keep]))
+    assert torch.isnan(got[perm[dropped]]).all()
+    assert native.device_status() == 0
+
+
+def test_wrapper_push_forward_equals_pull_forward(cuda):
+    from torch_ggml_ops_b200.peer_parallel import PeerExpertParallel
+
+    qt, E, N, K, tokens, top_k = ref.Q4_K, 8, 128, 256, 96, 4
+    w = to_dev(blocks.expert_weights(qt, E, N, K, 4))
+    ids = to_dev(torch.from_numpy(blocks.topk_routing(tokens, E, top_k, seed=2)))
+    x = to_dev(blocks.gaussian_bf16((tokens, K), 5))
+    outs = []
+    for push in (True, False):
+        pep = PeerExpertParallel(w, qt, E, N, K, capacity_rows=tokens * top_k, tokens_per_rank=tokens, top_k=top_k,
+                                 push_forward=push)
+        assert pep.push == push
+        plan = pep.plan(ids)
+        outs.append(pep.forward(plan, x).clone())
+        pep.check_overflow()
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(outs[0]), bits(outs[1]))
 
 
 def test_capacity_overflow_is_flagged_not_written(cuda):

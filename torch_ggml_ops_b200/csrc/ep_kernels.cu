@@ -233,6 +233,46 @@ __global__ void __launch_bounds__(256) ep_expand_kernel(const uint4* __restrict_
     }
 }
 
+// Token owner's side of the same scheme: result rows of routed pairs that were dropped (no room
+// in the expert's GPU) are never written by anybody; they are zeroed here, one warp per row.
+__global__ void __launch_bounds__(256) ep_zero_dropped_kernel(const int32_t* __restrict__ dst_rank, long long n_pairs,
+                                                              uint4* __restrict__ result, int vec_per_row) {
+    const long long warp = (blockIdx.x * 256LL + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= n_pairs || dst_rank[warp] >= 0) return;
+    for (int c = lane; c < vec_per_row; c += 32) result[warp * vec_per_row + c] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+// Owner side, for a forward whose epilogue returns every row to the token's owner
+// (tgo_grouped_fwd_rows): row_ptrs[row] = address, in this GPU's view of the owner's result buffer,
+// of the routed pair the row belongs to.  Row -> slot comes from row_slot, the pair's position s in
+// the token's top-k from slot_rows[slot][s] == row; slot = owner * tokens_per_rank + token, and the
+// pair's result row at the owner is token * top_k + s.  A row nobody announced gets a null pointer.
+__global__ void __launch_bounds__(256) ep_row_pointers_kernel(const int32_t* __restrict__ row_slot,
+                                                              const int32_t* __restrict__ slot_rows,
+                                                              const int32_t* __restrict__ n_rows, long long capacity,
+                                                              long long n_slots, int top_k, long long tokens_per_rank,
+                                                              const __grid_constant__ PeerPtrs result, long long row_bytes,
+                                                              unsigned long long* __restrict__ row_ptrs) {
+    long long n = *n_rows;
+    if (n > capacity) n = capacity;
+    for (long long row = blockIdx.x * 256LL + threadIdx.x; row < n; row += 256LL * gridDim.x) {
+        const long long slot = row_slot[row];
+        unsigned long long ptr = 0ull;
+        if (slot >= 0 && slot < n_slots) {
+            const long long owner = slot / tokens_per_rank, token = slot - owner * tokens_per_rank;
+            for (int s = 0; s < top_k; ++s) {
+                if (slot_rows[slot * top_k + s] == row) {
+                    ptr = reinterpret_cast<unsigned long long>(result.p[owner]) +
+                          static_cast<unsigned long long>((token * top_k + s) * row_bytes);
+                    break;
+                }
+            }
+        }
+        row_ptrs[row] = ptr;
+    }
+}
+
 // Owner side: part[slot][:] = sum over the slot's rows of rows[row][:] (fp32, rounded once); slots
 // without a row on this GPU are left alone (nobody reads them).
 __global__ void __launch_bounds__(256) ep_reduce_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ slot_rows,
@@ -491,6 +531,34 @@ int tgo_ep_expand(const void* token_buffer, int64_t n_slots, const int32_t* row_
     ep_expand_kernel<<<ep_grid(capacity * vec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(token_buffer), row_slot, n_rows_device, static_cast<uint4*>(rows), capacity, n_slots, vec);
     return ep_launch_check("ep_expand_kernel launch failed");
+}
+
+int tgo_ep_zero_dropped(const int32_t* dst_rank, int64_t n_pairs, void* result, int64_t width, void* stream) {
+    if (dst_rank == nullptr || result == nullptr) return route_fail(TGO_E_ARG, "null pointer");
+    if (n_pairs <= 0 || width <= 0 || (width * 2) % 16 != 0)
+        return route_fail(TGO_E_ARG, "zeroing dropped rows needs pairs > 0 and a row length that is a multiple of 8");
+    const long long blocks = (n_pairs * 32 + 255) / 256;
+    if (blocks > INT32_MAX) return route_fail(TGO_E_ARG, "too many routed pairs");
+    ep_zero_dropped_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        dst_rank, n_pairs, static_cast<uint4*>(result), static_cast<int>(width / 8));
+    return ep_launch_check("ep_zero_dropped_kernel launch failed");
+}
+
+int tgo_ep_row_pointers(const int32_t* row_slot, const int32_t* slot_rows, const int32_t* n_rows_device, int64_t capacity,
+                        int64_t n_slots, int64_t top_k, int64_t tokens_per_rank, void* const* result_ptrs, int64_t world,
+                        int64_t width, void** row_ptrs, void* stream) {
+    if (row_slot == nullptr || slot_rows == nullptr || n_rows_device == nullptr || row_ptrs == nullptr)
+        return route_fail(TGO_E_ARG, "null pointer");
+    if (capacity <= 0 || n_slots <= 0 || top_k <= 0 || tokens_per_rank <= 0 || width <= 0 || (width * 2) % 16 != 0 ||
+        n_slots != world * tokens_per_rank)
+        return route_fail(TGO_E_ARG, "row pointers need capacity > 0, slots = world * tokens_per_rank and a row length that is a multiple of 8");
+    PeerPtrs res = {};
+    const int rc = fill_peers(res, result_ptrs, world);
+    if (rc != TGO_OK) return rc;
+    ep_row_pointers_kernel<<<ep_grid(capacity), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        row_slot, slot_rows, n_rows_device, capacity, n_slots, static_cast<int>(top_k), tokens_per_rank, res, width * 2,
+        reinterpret_cast<unsigned long long*>(row_ptrs));
+    return ep_launch_check("ep_row_pointers_kernel launch failed");
 }
 
 int tgo_ep_reduce(const void* rows, const int32_t* slot_rows, int64_t n_slots, int64_t top_k, void* partial_sums,

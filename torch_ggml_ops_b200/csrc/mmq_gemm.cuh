@@ -147,6 +147,11 @@ struct GemmArgs {
     float* partial;                      // null: no split
     int nsplit;                          // 1: no split
     int split_steps;                     // steps per split (a multiple of the steps per stage)
+    // Forward of one weight set with scattered output rows: out_rows[r] is where row r of the result
+    // goes (any address this GPU can store to - its own memory or a peer's - 16-byte aligned, or null
+    // to drop the row).  The epilogue then stores straight there, which lets an expert-parallel step
+    // return every routed pair's row to the GPU that owns the token without a second pass.
+    __nv_bfloat16* const* out_rows;      // null: rows are contiguous in out[set]
 };
 
 // CG = 1: one CTA per tile of 128 weight rows.  CG = 2: a cluster of two CTAs works on 256 weight
@@ -956,6 +961,7 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
             const uint32_t taddr = tmem_base + acc * kTileTok + (static_cast<uint32_t>(quad * 32) << 16);
             const int mq = m0 + quad * 32;  // first output column of this warp
             __nv_bfloat16* out_base = args.out[MODE == kFwd ? set : 0] + static_cast<long long>(row0) * mdim;
+            const bool scatter = MODE == kFwd && args.out_rows != nullptr;
             if (SPLIT && args.partial != nullptr) {
                 // split reduction: fp32 partial sums, lane = output column (128 bytes per warp store)
                 const int m = mq + lane;
@@ -968,6 +974,52 @@ mmq_gemm_kernel(const __grid_constant__ GemmArgs args) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             if (c0 + j < ntok) part[static_cast<long long>(c0 + j) * mdim] = __uint_as_float(v[j]);
+                    }
+                }
+            } else if (MODE == kFwd && scatter) {
+                // Scattered rows (tgo_grouped_fwd_rows): every result row has its own destination,
+                // possibly in a peer GPU's memory.  A loop of its own, so that the ordinary epilogue
+                // below carries none of it.  Same staging tile as the transposing path; where the
+                // warp's 32 outputs do not all exist (last tile of weight rows) or rows are not
+                // 16-byte multiples, element-wise stores.
+                const bool vec_ok = (mdim & 7) == 0 && mq + 32 <= mdim;
+                uint8_t* stage = epi_g + (warp - kFirstEpilogueWarp) * (16 * 64);
+                const int wchunk = lane >> 2, wword = (lane & 3) << 2;
+                const int p = lane >> 2, part = lane & 3;
+                const uint8_t* rd0 = stage + p * 128 + (((2 * part) ^ (p & 1)) << 4);
+                const uint8_t* rd1 = stage + p * 128 + (((2 * part + 1) ^ (p & 1)) << 4);
+                for (int c0 = 16 * ehalf; c0 < ntok_pad; c0 += 4 * kEpilogueWarps) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + c0, v);
+                    tmem_ld_wait();
+                    if (vec_ok) {
+                        __nv_bfloat16* const* rp = args.out_rows + row0 + c0 + 2 * p;
+                        __nv_bfloat16* dst0 = c0 + 2 * p < ntok ? rp[0] : nullptr;
+                        __nv_bfloat16* dst1 = c0 + 2 * p + 1 < ntok ? rp[1] : nullptr;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            *reinterpret_cast<uint32_t*>(stage + q * 128 + (((wchunk ^ (q & 1)) << 4) | wword)) =
+                                pack_bf16(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
+                        __syncwarp();
+                        const uint4 a = *reinterpret_cast<const uint4*>(rd0);
+                        const uint4 b = *reinterpret_cast<const uint4*>(rd1);
+                        if (dst0 != nullptr)
+                            *reinterpret_cast<uint4*>(dst0 + mq + part * 8) =
+                                make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410),
+                                           __byte_perm(b.x, b.y, 0x5410), __byte_perm(b.z, b.w, 0x5410));
+                        if (dst1 != nullptr)
+                            *reinterpret_cast<uint4*>(dst1 + mq + part * 8) =
+                                make_uint4(__byte_perm(a.x, a.y, 0x7632), __byte_perm(a.z, a.w, 0x7632),
+                                           __byte_perm(b.x, b.y, 0x7632), __byte_perm(b.z, b.w, 0x7632));
+                        __syncwarp();
+                    } else if (mq + lane < mdim) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (c0 + j < ntok) {
+                                __nv_bfloat16* row = args.out_rows[row0 + c0 + j];
+                                if (row != nullptr) row[mq + lane] = __float2bfloat16(__uint_as_float(v[j]));
+                            }
+                        }
                     }
                 }
             } else if ((mdim & 7) == 0 && mq + 32 <= mdim) {

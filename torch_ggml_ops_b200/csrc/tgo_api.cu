@@ -455,6 +455,7 @@ struct Problem {
     int64_t groups;
     void* ws;
     int64_t ws_bytes;
+    void* const* out_rows;    // forward, one weight set: per-row destinations instead of out[0]
 };
 
 static int check_common(const Problem& p) {
@@ -476,6 +477,7 @@ static int check_common(const Problem& p) {
     }
     const int nouts = p.mode == kFwd ? p.nsets : 1;
     for (int s = 0; s < nouts; ++s) {
+        if (p.out_rows != nullptr) break;   // the rows go where the table says
         if (p.out[s] == nullptr) return fail(TGO_E_ARG, "null output pointer");
         if (!aligned16(p.out[s])) return fail(TGO_E_ARG, "output data pointer must be 16-byte aligned");
     }
@@ -514,6 +516,7 @@ static int run_problem(const Problem& p, cudaStream_t stream) {
     }
     a.wgt_row_bytes = static_cast<int>((p.K / 256) * bb);
     a.status = status_ptr();
+    a.out_rows = reinterpret_cast<__nv_bfloat16* const*>(p.out_rows);
     a.iq2s_grid = grid_ptr();
     if (a.status == nullptr || a.iq2s_grid == nullptr) return fail(TGO_E_CUDA, "cudaGetSymbolAddress failed");
     a.rows = static_cast<int>(p.rows);
@@ -782,6 +785,22 @@ int tgo_grouped_fwd(const void* x, const void* w0, const void* w1, void* y0, voi
     if (num_groups > num_experts) return fail(TGO_E_ARG, "active expert count exceeds packed expert count");
     Problem p = {};
     p.act[0] = x; p.wgt[0] = w0; p.wgt[1] = w1; p.out[0] = y0; p.out[1] = y1; p.nsets = w1 ? 2 : 1;
+    p.rows = rows; p.N = out_features; p.K = in_features; p.E = num_experts; p.qt = quant_type; p.mode = kFwd;
+    p.experts = expert_indices; p.offsets = expert_offsets; p.groups = num_groups;
+    p.ws = workspace; p.ws_bytes = workspace_bytes;
+    return run_problem(p, static_cast<cudaStream_t>(stream));
+}
+
+int tgo_grouped_fwd_rows(const void* x, const void* w, void* const* y_rows, const int64_t* expert_indices,
+                         const int32_t* expert_offsets, int64_t num_groups, int64_t num_experts, int64_t rows,
+                         int64_t out_features, int64_t in_features, int quant_type, void* workspace,
+                         int64_t workspace_bytes, void* stream) {
+    if (y_rows == nullptr) return fail(TGO_E_ARG, "null row-pointer table");
+    if (expert_indices == nullptr || expert_offsets == nullptr) return fail(TGO_E_ARG, "null routing pointer");
+    if (num_groups > num_experts) return fail(TGO_E_ARG, "active expert count exceeds packed expert count");
+    if ((out_features * 2) % 16 != 0) return fail(TGO_E_ARG, "scattered output rows need out_features to be a multiple of 8");
+    Problem p = {};
+    p.act[0] = x; p.wgt[0] = w; p.nsets = 1; p.out_rows = y_rows;
     p.rows = rows; p.N = out_features; p.K = in_features; p.E = num_experts; p.qt = quant_type; p.mode = kFwd;
     p.experts = expert_indices; p.offsets = expert_offsets; p.groups = num_groups;
     p.ws = workspace; p.ws_bytes = workspace_bytes;

@@ -48,6 +48,9 @@ SIGNATURES = {
     "tgo_ep_dispatch_tokens": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tgo_ep_expand": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp]),
     "tgo_ep_reduce": (_i32, [_vp, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "tgo_ep_zero_dropped": (_i32, [_vp, _i64, _vp, _i64, _vp]),
+    "tgo_ep_row_pointers": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _vp]),
+    "tgo_grouped_fwd_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
     "tgo_ep_pull_tokens": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tgo_grouped_fwd_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
 }
@@ -162,6 +165,15 @@ def grouped_fwd(x, w0, w1, y0, y1, expert_indices, expert_offsets, num_experts, 
                                 _ptr(expert_offsets), expert_indices.numel(), num_experts, rows, out_features,
                                 in_features, quant_type, _ptr(workspace), workspace.numel(), _stream(stream)),
           "tgo_grouped_fwd")
+
+
+def grouped_fwd_rows(x, w, y_row_ptrs, expert_indices, expert_offsets, num_experts, rows, out_features, in_features,
+                     quant_type, workspace, stream=None) -> None:
+    """Grouped forward of one projection whose result row r is stored at the address ``y_row_ptrs[r]``
+    (int64 device tensor of ``rows`` addresses, 0 = drop the row); see ``tgo_grouped_fwd_rows``."""
+    check(lib().tgo_grouped_fwd_rows(_ptr(x), _ptr(w), _ptr(y_row_ptrs), _ptr(expert_indices), _ptr(expert_offsets),
+                                     expert_indices.numel(), num_experts, rows, out_features, in_features, quant_type,
+                                     _ptr(workspace), workspace.numel(), _stream(stream)), "tgo_grouped_fwd_rows")
 
 
 def grouped_dx(dy0, dy1, w0, w1, dx, expert_indices, expert_offsets, num_experts, rows, out_features, in_features,
@@ -315,6 +327,22 @@ def ep_expand(token_buffer, row_slot, n_rows_device, rows, stream=None) -> None:
     """rows[r] = token_buffer[row_slot[r]] for r < n_rows_device[0] (a device int32 tensor)."""
     check(lib().tgo_ep_expand(_ptr(token_buffer), token_buffer.shape[0], _ptr(row_slot), _ptr(n_rows_device),
                               _ptr(rows), rows.shape[0], rows.shape[1], _stream(stream)), "tgo_ep_expand")
+
+
+def ep_zero_dropped(dst_rank, result, stream=None) -> None:
+    """result[i] = 0 for the routed pairs with dst_rank[i] < 0 (``tgo_ep_zero_dropped``)."""
+    check(lib().tgo_ep_zero_dropped(_ptr(dst_rank), dst_rank.numel(), _ptr(result), result.shape[1], _stream(stream)),
+          "tgo_ep_zero_dropped")
+
+
+def ep_row_pointers(row_slot, slot_rows, n_rows_device, top_k, tokens_per_rank, result_ptrs, width, row_ptrs,
+                    stream=None) -> None:
+    """row_ptrs[r] (int64 device tensor [capacity]) = address of the result row, at the token's owner, of
+    the routed pair that expert-major row r belongs to; ``result_ptrs``: this GPU's addresses of every
+    rank's [tokens_per_rank * top_k, width] result buffer.  See ``tgo_ep_row_pointers``."""
+    check(lib().tgo_ep_row_pointers(_ptr(row_slot), _ptr(slot_rows), _ptr(n_rows_device), row_ptrs.shape[0],
+                                    slot_rows.shape[0], top_k, tokens_per_rank, _ptr_array(result_ptrs),
+                                    len(result_ptrs), width, _ptr(row_ptrs), _stream(stream)), "tgo_ep_row_pointers")
 
 
 def ep_reduce(rows, slot_rows, top_k, partial_sums, stream=None) -> None:

@@ -44,10 +44,13 @@ class PeerExpertParallel:
 
     def __init__(self, local_weight: torch.Tensor, quant_type: int, num_experts: int, out_features: int,
                  in_features: int, capacity_rows: int, group=None, tokens_per_rank: int | None = None,
-                 top_k: int | None = None, fences: str = "peer"):
+                 top_k: int | None = None, fences: str = "peer", push_forward: bool = True):
         """``fences``: how the ranks' phases are ordered - "peer": this library's barrier kernel over
         peer memory (bounded wait, no collective library in the step); "nccl": one-element all-reduces
-        and an all-gather of the counts."""
+        and an all-gather of the counts.  ``push_forward`` (token-level exchange only): the forward
+        matmul's epilogue stores every routed pair's row straight into the memory of the GPU that owns
+        the token (tgo_grouped_fwd_rows), instead of a local result buffer that the owners pull from
+        afterwards; ``forward`` then returns a view of this rank's result buffer."""
         if fences not in ("peer", "nccl"):
             raise ValueError("fences must be 'peer' or 'nccl'")
         self.fences = fences
@@ -74,6 +77,8 @@ class PeerExpertParallel:
             slots = self.world * self.tpr
             shapes.update({"tok_in": (slots, self.K, torch.bfloat16), "dx_part": (slots, self.K, torch.bfloat16),
                            "row_slot": (self.cap, 1, torch.int32), "slot_rows": (slots, self.top_k, torch.int32)})
+            if push_forward and self.N % 8 == 0:
+                shapes["y_tok"] = (self.tpr * self.top_k, self.N, torch.bfloat16)
         self.buf, self.peers = {}, {}
         if self.world > 1:
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -101,6 +106,9 @@ class PeerExpertParallel:
             # fills before anybody goes on
             torch.cuda.synchronize()
             dist.barrier(group=group)
+        self.push = "y_tok" in self.buf
+        if self.push:
+            self.row_ptrs = torch.zeros(self.cap, dtype=torch.int64, device=dev)
         self.ws = torch.empty(native.grouped_workspace_bytes(self.cap, self.EL), dtype=torch.uint8, device=dev)
         self._token = torch.zeros(1, dtype=torch.int32, device=dev)
         self.overflow = None
@@ -168,6 +176,9 @@ class PeerExpertParallel:
                                  self.peers["row_slot"], self.peers["slot_rows"])
             plan["token_level"] = True
             plan["n_rows"] = lo[self.EL - 1:]   # device int32: rows that exist in this rank's buffers
+            if self.push:
+                # nobody writes the result rows of dropped pairs: they read as zeros
+                native.ep_zero_dropped(dst_rank, self.buf["y_tok"][: plan["tokens"] * self.top_k])
         return plan
 
     def check_overflow(self) -> None:
@@ -183,6 +194,21 @@ class PeerExpertParallel:
         """[tokens, K] bf16 -> [tokens * top_k, N]: every routed pair's expert projection
         (written to ``out`` when given)."""
         k = plan["top_k"]
+        if plan["token_level"] and self.push:
+            native.ep_dispatch_tokens(x_tokens, plan["dst_rank"], k, self.rank, self.tpr, self.peers["tok_in"])
+            self._fence()
+            native.ep_expand(self.buf["tok_in"], self.buf["row_slot"], plan["n_rows"], self.buf["x_in"])
+            native.ep_row_pointers(self.buf["row_slot"], self.buf["slot_rows"], plan["n_rows"], k, self.tpr,
+                                   self.peers["y_tok"], self.N, self.row_ptrs)
+            # the matmul's epilogue returns every row to the token's owner (plain 16-byte peer stores)
+            native.grouped_fwd_rows(self.buf["x_in"], self.weight, self.row_ptrs, plan["indices"], plan["offsets"],
+                                    self.EL, self.cap, self.N, self.K, self.qt, self.ws)
+            self._fence()
+            y = self.buf["y_tok"][: x_tokens.shape[0] * k]
+            if out is not None:
+                out.copy_(y)
+                return out
+            return y
         if plan["token_level"]:
             native.ep_dispatch_tokens(x_tokens, plan["dst_rank"], k, self.rank, self.tpr, self.peers["tok_in"])
             self._fence()
