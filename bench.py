@@ -449,10 +449,12 @@ def gpu_arm(args):
         ms_step = timed_steps(step_ep, args.steps)
         clocks = sampler.stop()
         # this library's kernels per step: GEMMs + tile builders (4), routing sort (3), plan (2, + 1 for the
-        # token maps), exchange (pair level 4; token level 6: dispatch, expand, pull y, dispatch dy, reduce, pull)
-        launches = 4 + 3 + (3 + 6 if args.token_level else 2 + 4) + (6 if args.fences == "peer" else 0)   # + count exchange, 5 barriers
-        executor = (f"{world} GPUs: experts sharded; dispatch/combine by peer-memory kernels over NVLink (NCCL only for "
-                    "the host-side setup; counts and phase barriers by peer memory too unless --fences nccl)")
+        # token maps, zeroing of dropped rows), exchange (pair level 4; token level 6: dispatch, expand, row
+        # pointers, dispatch dy, reduce, pull - the forward rows are returned by the matmul's own epilogue)
+        launches = 4 + 3 + (4 + 6 if args.token_level else 2 + 4) + (6 if args.fences == "peer" else 0)   # + count exchange, 5 barriers
+        executor = (f"{world} GPUs: experts sharded; dispatch/combine by peer-memory kernels over NVLink, forward rows "
+                    "stored into the token owner's memory by the matmul epilogue (NCCL only for the host-side setup; "
+                    "counts and phase barriers by peer memory too unless --fences nccl)")
     result["device_status"] = native.device_status()
     result["ep_overflow"] = int(pep.overflow.item())
 
