@@ -466,6 +466,10 @@ def gpu_arm(args):
     par["tolerance"] = {"fwd": 1e-2, "dx": 5e-3}
     par["ranks_checked"] = world
     result["parity"] = par
+    if pep.push:
+        # one more step, not timed, with a CUDA event after every phase (max over ranks, ms)
+        ph = pep.phase_times(step_ep)
+        result["ep_phases_ms"] = {k: round(max_over_ranks(v), 4) for k, v in ph.items()}
 
     # ---------------------------------------------------------------- end to end with host buffers (every N)
     # Tokens and per-pair cotangents come from pinned host memory, per-pair forward rows and

@@ -113,6 +113,29 @@ class PeerExpertParallel:
         self._token = torch.zeros(1, dtype=torch.int32, device=dev)
         self.overflow = None
         self._plan_bufs = None   # routing outputs are reused from step to step (stream-ordered)
+        self.marks = None        # set to a list to collect (phase name, CUDA event) pairs, see `phase_times`
+
+    # ------------------------------------------------------------------ phase timing (diagnostics)
+    def _mark(self, name: str) -> None:
+        if self.marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.marks.append((name, ev))
+
+    def phase_times(self, step) -> dict:
+        """Runs ``step()`` (a callable that calls plan / forward / grad_input of this object) once with a
+        CUDA event after every phase and returns {phase: milliseconds} on this rank.  Not for timed
+        regions: the events add launches."""
+        step()            # keeps the GPU busy while the marked step is enqueued (the host stays ahead, as in a loop)
+        self.marks = []
+        self._mark("start")
+        step()
+        torch.cuda.synchronize()
+        marks, self.marks = self.marks, None
+        out = {}
+        for (_, e0), (name, e1) in zip(marks[:-1], marks[1:]):
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        return out
 
     # ------------------------------------------------------------------ ordering between ranks
     def _fence(self) -> None:
@@ -167,6 +190,7 @@ class PeerExpertParallel:
         else:
             counts_all = b["counts"].reshape(1, self.E)
         dst_rank, dst_row, li, lo, overflow = native.ep_plan(counts_all, self.rank, flat, p2s, self.cap, out=b)
+        self._mark("plan")
         self.overflow = overflow  # device flag: a row did not fit in `capacity_rows` (read it when convenient)
         plan = {"top_k": topk_ids.shape[1], "tokens": topk_ids.shape[0], "dst_rank": dst_rank, "dst_row": dst_row,
                 "indices": li, "offsets": lo, "token_level": False}
@@ -179,6 +203,7 @@ class PeerExpertParallel:
             if self.push:
                 # nobody writes the result rows of dropped pairs: they read as zeros
                 native.ep_zero_dropped(dst_rank, self.buf["y_tok"][: plan["tokens"] * self.top_k])
+        self._mark("plan")
         return plan
 
     def check_overflow(self) -> None:
@@ -196,14 +221,19 @@ class PeerExpertParallel:
         k = plan["top_k"]
         if plan["token_level"] and self.push:
             native.ep_dispatch_tokens(x_tokens, plan["dst_rank"], k, self.rank, self.tpr, self.peers["tok_in"])
+            self._mark("dispatch_tokens")
             self._fence()
+            self._mark("barriers")
             native.ep_expand(self.buf["tok_in"], self.buf["row_slot"], plan["n_rows"], self.buf["x_in"])
             native.ep_row_pointers(self.buf["row_slot"], self.buf["slot_rows"], plan["n_rows"], k, self.tpr,
                                    self.peers["y_tok"], self.N, self.row_ptrs)
+            self._mark("expand")
             # the matmul's epilogue returns every row to the token's owner (plain 16-byte peer stores)
             native.grouped_fwd_rows(self.buf["x_in"], self.weight, self.row_ptrs, plan["indices"], plan["offsets"],
                                     self.EL, self.cap, self.N, self.K, self.qt, self.ws)
+            self._mark("forward_matmul_and_return")
             self._fence()
+            self._mark("barriers")
             y = self.buf["y_tok"][: x_tokens.shape[0] * k]
             if out is not None:
                 out.copy_(y)
@@ -231,15 +261,21 @@ class PeerExpertParallel:
         slots of each token (optionally weighted), fp32 accumulation, one bf16 rounding."""
         k = plan["top_k"]
         native.ep_dispatch(dy_pairs, 1, plan["dst_rank"], plan["dst_row"], self.peers["dy_in"])
+        self._mark("dispatch_dy")
         self._fence()
+        self._mark("barriers")
         native.grouped_dx(self.buf["dy_in"], None, self.weight, None, self.buf["dx_out"], plan["indices"],
                           plan["offsets"], self.EL, self.cap, self.N, self.K, self.qt, self.ws)
         dx = out if out is not None else torch.empty(dy_pairs.shape[0] // k, self.K, dtype=torch.bfloat16,
                                                       device=self.device)
         if plan["token_level"] and weights is None:
+            self._mark("dx_matmul")
             native.ep_reduce(self.buf["dx_out"], self.buf["slot_rows"], k, self.buf["dx_part"])
+            self._mark("reduce")
             self._fence()
+            self._mark("barriers")
             native.ep_pull_tokens(self.peers["dx_part"], plan["dst_rank"], k, self.rank, self.tpr, dx)
+            self._mark("pull_partial_sums")
             return dx
         self._fence()
         w = None if weights is None else weights.reshape(-1).float().contiguous()
