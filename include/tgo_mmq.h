@@ -283,6 +283,13 @@ int tgo_ep_expand(const void* token_buffer, int64_t n_slots, const int32_t* row_
                   void* stream);
 int tgo_ep_zero_dropped(const int32_t* dst_rank, int64_t n_pairs, void* result, int64_t width,
                         void* stream);
+/* tgo_ep_token_maps + tgo_ep_zero_dropped as one launch (the same fusion of tgo_ep_expand with
+ * tgo_ep_row_pointers was measured and is slower than the two launches: the pointer look-up
+ * stalls the copy) */
+int tgo_ep_token_maps_rows(const int32_t* dst_rank, const int32_t* dst_row, int64_t tokens, int64_t top_k,
+                           int64_t my_rank, int64_t tokens_per_rank, void* const* row_slot_ptrs,
+                           void* const* slot_rows_ptrs, int64_t world, void* result,
+                           int64_t result_width, void* stream);
 int tgo_ep_row_pointers(const int32_t* row_slot, const int32_t* slot_rows, const int32_t* n_rows_device,
                         int64_t capacity, int64_t n_slots, int64_t top_k, int64_t tokens_per_rank,
                         void* const* result_ptrs, int64_t world, int64_t width, void** row_ptrs,

@@ -143,6 +143,24 @@ def test_scattered_rows_null_pointers_and_odd_widths(cuda, N):
     assert native.device_status() == 0
 
 
+def test_token_maps_rows_zeroes_the_rows_of_dropped_pairs(cuda):
+    from torch_ggml_ops_b200 import native
+
+    tokens, top_k, cap, N = 6, 2, 16, 64
+    dst_rank = torch.tensor([0, -1, 0, 0, -1, 0, 0, 0, 0, -1, 0, 0], dtype=torch.int32, device="cuda")
+    dst_row = torch.tensor([0, -1, 1, 2, -1, 3, 4, 5, 6, -1, 7, 8], dtype=torch.int32, device="cuda")
+    row_slot = torch.full((cap,), -1, dtype=torch.int32, device="cuda")
+    slot_rows = torch.full((tokens, top_k), -9, dtype=torch.int32, device="cuda")
+    result = torch.full((tokens * top_k, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    native.ep_token_maps_rows(dst_rank, dst_row, tokens, top_k, 0, tokens, [row_slot.data_ptr()], [slot_rows.data_ptr()], result)
+    torch.cuda.synchronize()
+    dropped = (dst_rank < 0).cpu()
+    assert int(torch.count_nonzero(result.cpu()[dropped].float())) == 0 and not torch.isnan(result.cpu()[dropped]).any()
+    assert torch.isnan(result.cpu()[~dropped]).all()
+    assert slot_rows.reshape(-1).cpu().tolist() == dst_row.cpu().tolist()
+    assert row_slot[:9].cpu().tolist() == [0, 1, 1, 2, 3, 3, 4, 5, 5]
+
+
 def test_wrapper_push_forward_equals_pull_forward(cuda):
     from torch_ggml_ops_b200.peer_parallel import PeerExpertParallel
 

@@ -181,7 +181,8 @@ __global__ void __launch_bounds__(256) ep_token_maps_kernel(const int32_t* __res
                                                             const __grid_constant__ PeerPtrs row_slot,
                                                             const __grid_constant__ PeerPtrs slot_rows,
                                                             const float* __restrict__ pair_weights,
-                                                            const __grid_constant__ PeerPtrs row_weight) {
+                                                            const __grid_constant__ PeerPtrs row_weight,
+                                                            uint4* __restrict__ result, int result_vec) {
     const long long i = blockIdx.x * 256LL + threadIdx.x;
     if (i >= n_pairs) return;
     const long long t = i / top_k;
@@ -193,6 +194,9 @@ __global__ void __launch_bounds__(256) ep_token_maps_kernel(const int32_t* __res
         static_cast<int32_t*>(row_slot.p[r])[row] = static_cast<int32_t>(slot);
         // the pair's routing weight travels with the map, so the owner can scale the row it computes
         if (pair_weights != nullptr) static_cast<float*>(row_weight.p[r])[row] = pair_weights[i];
+    } else if (result != nullptr) {
+        // a dropped pair (no room on its expert's GPU): nobody writes its result row, it reads as zeros
+        for (int c = 0; c < result_vec; ++c) result[i * result_vec + c] = make_uint4(0u, 0u, 0u, 0u);
     }
 }
 
@@ -483,9 +487,10 @@ int tgo_ep_pull(void* const* peer_ptrs, int64_t world, const int32_t* dst_rank, 
     return ep_launch_check("ep_pull_kernel launch failed");
 }
 
-int tgo_ep_token_maps(const int32_t* dst_rank, const int32_t* dst_row, int64_t tokens, int64_t top_k, int64_t my_rank,
+static int token_maps(const int32_t* dst_rank, const int32_t* dst_row, int64_t tokens, int64_t top_k, int64_t my_rank,
                       int64_t tokens_per_rank, void* const* row_slot_ptrs, void* const* slot_rows_ptrs,
-                      const float* pair_weights, void* const* row_weight_ptrs, int64_t world, void* stream) {
+                      const float* pair_weights, void* const* row_weight_ptrs, int64_t world, void* result,
+                      int64_t result_width, void* stream) {
     if (dst_rank == nullptr || dst_row == nullptr) return route_fail(TGO_E_ARG, "null pointer");
     if (tokens <= 0 || top_k <= 0 || top_k > 1024 || tokens > tokens_per_rank || my_rank < 0 || my_rank >= world ||
         tokens_per_rank * world * top_k > INT32_MAX)
@@ -500,8 +505,24 @@ int tgo_ep_token_maps(const int32_t* dst_rank, const int32_t* dst_row, int64_t t
     const long long n_pairs = tokens * top_k;
     ep_token_maps_kernel<<<static_cast<int>((n_pairs + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         dst_rank, dst_row, n_pairs, static_cast<int>(top_k), static_cast<int>(world), my_rank * tokens_per_rank, rs, sr,
-        pair_weights, rw);
+        pair_weights, rw, static_cast<uint4*>(result), static_cast<int>(result_width / 8));
     return ep_launch_check("ep_token_maps_kernel launch failed");
+}
+
+int tgo_ep_token_maps(const int32_t* dst_rank, const int32_t* dst_row, int64_t tokens, int64_t top_k, int64_t my_rank,
+                      int64_t tokens_per_rank, void* const* row_slot_ptrs, void* const* slot_rows_ptrs,
+                      const float* pair_weights, void* const* row_weight_ptrs, int64_t world, void* stream) {
+    return token_maps(dst_rank, dst_row, tokens, top_k, my_rank, tokens_per_rank, row_slot_ptrs, slot_rows_ptrs, pair_weights,
+                      row_weight_ptrs, world, nullptr, 0, stream);
+}
+
+int tgo_ep_token_maps_rows(const int32_t* dst_rank, const int32_t* dst_row, int64_t tokens, int64_t top_k, int64_t my_rank,
+                           int64_t tokens_per_rank, void* const* row_slot_ptrs, void* const* slot_rows_ptrs,
+                           int64_t world, void* result, int64_t result_width, void* stream) {
+    if (result == nullptr || result_width <= 0 || (result_width * 2) % 16 != 0)
+        return route_fail(TGO_E_ARG, "the result buffer needs a row length that is a multiple of 8");
+    return token_maps(dst_rank, dst_row, tokens, top_k, my_rank, tokens_per_rank, row_slot_ptrs, slot_rows_ptrs, nullptr,
+                      nullptr, world, result, result_width, stream);
 }
 
 int tgo_ep_dispatch_tokens(const void* src, const int32_t* dst_rank, int64_t tokens, int64_t top_k, int64_t width,

@@ -48,6 +48,7 @@ SIGNATURES = {
     "tgo_ep_dispatch_tokens": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "tgo_ep_expand": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp]),
     "tgo_ep_reduce": (_i32, [_vp, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "tgo_ep_token_maps_rows": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _i64, _vp]),
     "tgo_ep_zero_dropped": (_i32, [_vp, _i64, _vp, _i64, _vp]),
     "tgo_ep_row_pointers": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _vp]),
     "tgo_grouped_fwd_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
@@ -327,6 +328,15 @@ def ep_expand(token_buffer, row_slot, n_rows_device, rows, stream=None) -> None:
     """rows[r] = token_buffer[row_slot[r]] for r < n_rows_device[0] (a device int32 tensor)."""
     check(lib().tgo_ep_expand(_ptr(token_buffer), token_buffer.shape[0], _ptr(row_slot), _ptr(n_rows_device),
                               _ptr(rows), rows.shape[0], rows.shape[1], _stream(stream)), "tgo_ep_expand")
+
+
+def ep_token_maps_rows(dst_rank, dst_row, tokens, top_k, my_rank, tokens_per_rank, row_slot_ptrs, slot_rows_ptrs, result,
+                       stream=None) -> None:
+    """``ep_token_maps`` that also zeroes the rows of ``result`` ([tokens * top_k, width]) whose routed pair was
+    dropped (``tgo_ep_token_maps_rows``)."""
+    check(lib().tgo_ep_token_maps_rows(_ptr(dst_rank), _ptr(dst_row), tokens, top_k, my_rank, tokens_per_rank,
+                                       _ptr_array(row_slot_ptrs), _ptr_array(slot_rows_ptrs), len(row_slot_ptrs),
+                                       _ptr(result), result.shape[1], _stream(stream)), "tgo_ep_token_maps_rows")
 
 
 def ep_zero_dropped(dst_rank, result, stream=None) -> None:

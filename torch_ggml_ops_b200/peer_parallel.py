@@ -196,13 +196,16 @@ class PeerExpertParallel:
                 "indices": li, "offsets": lo, "token_level": False}
         if self.token_level:
             # the peers' maps are rewritten here; the exchanges that read them come after a fence
-            native.ep_token_maps(dst_rank, dst_row, plan["tokens"], self.top_k, self.rank, self.tpr,
-                                 self.peers["row_slot"], self.peers["slot_rows"])
+            if self.push:
+                # nobody writes the result rows of dropped pairs: the same launch zeroes them
+                native.ep_token_maps_rows(dst_rank, dst_row, plan["tokens"], self.top_k, self.rank, self.tpr,
+                                          self.peers["row_slot"], self.peers["slot_rows"],
+                                          self.buf["y_tok"][: plan["tokens"] * self.top_k])
+            else:
+                native.ep_token_maps(dst_rank, dst_row, plan["tokens"], self.top_k, self.rank, self.tpr,
+                                     self.peers["row_slot"], self.peers["slot_rows"])
             plan["token_level"] = True
             plan["n_rows"] = lo[self.EL - 1:]   # device int32: rows that exist in this rank's buffers
-            if self.push:
-                # nobody writes the result rows of dropped pairs: they read as zeros
-                native.ep_zero_dropped(dst_rank, self.buf["y_tok"][: plan["tokens"] * self.top_k])
         self._mark("plan")
         return plan
 
