@@ -317,6 +317,10 @@ def gpu_arm(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # NCCL serves the host-side setup and the few scalar reductions around the timed region only;
+        # without NVLS it binds no NVLink multicast object to the buffers (a rank that dies while one
+        # is bound can fault its peers)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     qt, E, N, K, T, top_k = wl["qt"], wl["experts"], wl["N"], wl["K"], wl["tokens"], wl["top_k"]
     seed = 2024
