@@ -23,16 +23,16 @@
 //
 // Warp roles (768 threads; backward - forward places them differently, see the kernel): 0 activation
 // producer (TMA), 1 UMMA issuer + TMEM owner, 2 and 3 raw weight producers (TMA, alternate stages),
-// 4-19 decode (groups of warps on alternate 64-element steps: four
-// groups of 4 for Q4_K / Q5_K, two groups of 8 otherwise), 20-23 epilogue (TMEM -> bf16 -> global).
+// 4-19 decode (groups of warps on alternate 64-element steps: four groups of 4 for Q4_K / Q5_K, two
+// groups of 8 otherwise), 20-23 epilogue (TMEM -> bf16 -> global, or to per-row destinations).
 //
 // Wide tiles.  A tile of more than 256 tokens (up to 512) is split into two halves that use both
 // accumulators at once and share every decoded weight step: each decoded stage is consumed by two
 // consecutive pipeline stages (half 0 -> accumulator a, half 1 -> accumulator a ^ 1), so the
 // decode work per output element halves.  The epilogue sees the halves as two ordinary tiles.
 //
-// Synchronisation.  A stage is KS steps (1 for a single CTA, 2 for a pair: one step per decode
-// group); pipeline stages have running index j over all tiles of the CTA (a wide tile has two
+// Synchronisation.  A stage is KS steps (1 for a single CTA, 2 for a pair; each step is decoded by
+// one decode group); pipeline stages have running index j over all tiles of the CTA (a wide tile has two
 // pipeline stages per decoded stage):
 //   full[j % NB]  <- the activation TMA (expect_tx for the whole stage, announced by the leader)
 //                    and the decode warps of the stage's steps (of both CTAs); the UMMA issuer
