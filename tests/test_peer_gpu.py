@@ -282,3 +282,24 @@ def test_rank_barrier_and_count_exchange_kernels(cuda):
     assert native.device_status() == 0
     x = torch.ones(8, device="cuda") * 2                      # the context still works
     assert float(x.sum()) == 16.0
+
+
+def test_phase_times_reports_every_phase_of_a_step(cuda):
+    from torch_ggml_ops_b200.peer_parallel import PeerExpertParallel
+
+    qt, E, N, K, tokens, top_k = ref.Q4_K, 8, 128, 256, 64, 4
+    w = to_dev(blocks.expert_weights(qt, E, N, K, 4))
+    ids = to_dev(torch.from_numpy(blocks.topk_routing(tokens, E, top_k, seed=2)))
+    x = to_dev(blocks.gaussian_bf16((tokens, K), 5))
+    dy = to_dev(blocks.gaussian_bf16((tokens * top_k, N), 6))
+    pep = PeerExpertParallel(w, qt, E, N, K, capacity_rows=tokens * top_k, tokens_per_rank=tokens, top_k=top_k)
+
+    def step():
+        plan = pep.plan(ids)
+        pep.forward(plan, x)
+        pep.grad_input(plan, dy)
+
+    ph = pep.phase_times(step)
+    assert set(ph) == {"plan", "dispatch_tokens", "barriers", "expand", "forward_matmul_and_return", "dispatch_dy",
+                       "dx_matmul", "reduce", "pull_partial_sums"}
+    assert all(v >= 0.0 for v in ph.values()) and pep.marks is None
