@@ -373,7 +373,8 @@ def gpu_arm(args):
         matmul epilogues of the experts' GPUs store them there); ``keep`` copies them to a private
         buffer, for a reader that overlaps the next step (the end-to-end loop's copy-out stream)."""
         plan = pep.plan(ids32)
-        y = pep.forward(plan, x, out=y_out[b] if keep else None)
+        # the barrier after the forward is the one inside grad_input (the rows are complete after it)
+        y = pep.forward(plan, x, out=y_out[b] if keep else None, fence=False)
         pep.grad_input(plan, dy, out=dx_out[b])
         return y, dx_out[b]
 
@@ -455,7 +456,7 @@ def gpu_arm(args):
         # this library's kernels per step: GEMMs + tile builders (4), routing sort (3), plan (2, + 1 for the
         # token maps, zeroing of dropped rows), exchange (pair level 4; token level 6: dispatch, expand, row
         # pointers, dispatch dy, reduce, pull - the forward rows are returned by the matmul's own epilogue)
-        launches = 4 + 3 + (4 + 6 if args.token_level else 2 + 4) + (6 if args.fences == "peer" else 0)   # + count exchange, 5 barriers
+        launches = 4 + 3 + (4 + 6 if args.token_level else 2 + 4) + (5 if args.fences == "peer" else 0)   # + count exchange, 4 barriers
         executor = (f"{world} GPUs: experts sharded; dispatch/combine by peer-memory kernels over NVLink, forward rows "
                     "stored into the token owner's memory by the matmul epilogue (NCCL only for the host-side setup; "
                     "counts and phase barriers by peer memory too unless --fences nccl)")

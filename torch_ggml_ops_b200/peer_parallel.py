@@ -218,9 +218,12 @@ class PeerExpertParallel:
                                "this routing; dropped pairs were computed as zeros")
 
     # ------------------------------------------------------------------ forward
-    def forward(self, plan, x_tokens: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, plan, x_tokens: torch.Tensor, out: torch.Tensor | None = None, fence: bool = True) -> torch.Tensor:
         """[tokens, K] bf16 -> [tokens * top_k, N]: every routed pair's expert projection
-        (written to ``out`` when given)."""
+        (written to ``out`` when given).  ``fence=False`` (only with the forward that returns its own
+        rows, and without ``out``): the call ends without the rank barrier, so the rows that peers store
+        into the returned buffer are complete only after this object's next barrier - the one inside
+        ``grad_input`` when that follows, as in a training step."""
         k = plan["top_k"]
         if plan["token_level"] and self.push:
             native.ep_dispatch_tokens(x_tokens, plan["dst_rank"], k, self.rank, self.tpr, self.peers["tok_in"])
@@ -235,8 +238,9 @@ class PeerExpertParallel:
             native.grouped_fwd_rows(self.buf["x_in"], self.weight, self.row_ptrs, plan["indices"], plan["offsets"],
                                     self.EL, self.cap, self.N, self.K, self.qt, self.ws)
             self._mark("forward_matmul_and_return")
-            self._fence()
-            self._mark("barriers")
+            if fence or out is not None:
+                self._fence()
+                self._mark("barriers")
             y = self.buf["y_tok"][: x_tokens.shape[0] * k]
             if out is not None:
                 out.copy_(y)
