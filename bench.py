@@ -15,8 +15,11 @@ One step = one forward pass plus one input-gradient pass over the routed rows.
   resident in HBM (C-ABI calls, CUDA events per launch).
 * N > 1 (under torchrun): expert-parallel.  Each rank owns 256/N experts and 8192 tokens; a token's
   row goes once to every GPU that owns one of its experts and results come back, moved by this
-  library's peer-memory kernels over NVLink (NCCL carries only the per-expert counts and the
-  one-element fences between phases).  Weak scaling: per-GPU tokens are fixed.
+  library's peer-memory kernels over NVLink; the forward matmul's epilogue stores its rows
+  straight into the token owner's memory; counts and phase barriers go over peer memory too
+  (NCCL only for the host-side setup and the scalar reductions around the timed region, or with
+  ``--fences nccl``).  Weak scaling: per-GPU tokens are fixed.  ``ep_phases_ms`` is the CUDA-event
+  time of every phase of one extra, untimed step.
 * every N: ``e2e`` is the expert-parallel step (tokens + top-k ids in, per-pair forward rows and
   per-token gradients out; routing sort, dispatch and combine inside) with pinned host buffers
   copied in and results copied out inside the timed region; ``parity`` compares sampled tokens of
