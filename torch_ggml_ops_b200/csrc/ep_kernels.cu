@@ -287,27 +287,17 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const uint4* __restrict_
         const int c = static_cast<int>(v - slot * vec_per_row);
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         bool any = false;
-        // eight pairs at a time: first the row indices, then all the row loads (independent, so up
-        // to eight are in flight per thread), then the sums in the pairs' order
-        for (int s0 = 0; s0 < top_k; s0 += 8) {
-            int row[8];
-            uint4 val[8];
+        for (int s = 0; s < top_k; ++s) {
+            const int row = slot_rows[slot * top_k + s];
+            if (row < 0) continue;
+            any = true;
+            const uint4 val = rows[static_cast<long long>(row) * vec_per_row + c];
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&val);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) row[i] = s0 + i < top_k ? slot_rows[slot * top_k + s0 + i] : -1;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                val[i] = row[i] >= 0 ? rows[static_cast<long long>(row[i]) * vec_per_row + c] : make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if (row[i] < 0) continue;
-                any = true;
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&val[i]);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 f = __bfloat1622float2(h[j]);
-                    acc[2 * j] += f.x;
-                    acc[2 * j + 1] += f.y;
-                }
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
             }
         }
         if (!any) continue;
